@@ -16,11 +16,10 @@ else
   bash tools/gpu_launchlist.sh > gpurun_out/r02_launches_decode.txt 2>&1; tail -10 gpurun_out/r02_launches_decode.txt
   # one --set full capture per shape; only the CSV pages travel back (two .ncu-rep files exceed gpurun's 64 MiB), the large shape keeps its report
   for shp in 51200x5120 10240x5120; do
-    timeout 600 ncu --set full --clock-control none --import-source on -k regex:kf_gemv_kernel -s 6 -c 1 -f -o /tmp/r02_gemv_q4_fast_$shp \
+    timeout 600 ncu --set full --clock-control none -k regex:kf_gemv_kernel -s 6 -c 1 -f -o /tmp/r02_gemv_q4_fast_$shp \
       python tools/gemv_bench.py --shapes $shp --ms 1 --types q4 --exact 0 --tc 0 --iters 4 > gpurun_out/r02_ncu_gemv_$shp.log 2>&1
     ncu -i /tmp/r02_gemv_q4_fast_$shp.ncu-rep --page raw --csv > gpurun_out/r02_ncu_gemv_q4_fast_${shp}_raw.csv 2>/dev/null
     ncu -i /tmp/r02_gemv_q4_fast_$shp.ncu-rep --page details --csv > gpurun_out/r02_ncu_gemv_q4_fast_${shp}_details.csv 2>/dev/null
   done
-  ncu -i /tmp/r02_gemv_q4_fast_51200x5120.ncu-rep --page source --csv > gpurun_out/r02_ncu_gemv_q4_fast_51200x5120_source.csv 2>/dev/null
   ls -la gpurun_out | tail -12
 fi
