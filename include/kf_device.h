@@ -249,6 +249,40 @@ int kf_tp_begin(kf_ctx* ctx);
 int kf_exchange_fused_ready(kf_ctx* ctx, int M, int cols);
 int kf_linear_exchange(kf_ctx* ctx, void* y_dev, const kf_tensor_desc* w, const void* x_dev, int M, const void* residual_dev);
 
+/* ---- 32-bit residual stream, general-shape matmuls, state-space and latent-attention mixers, expert routing (linear_g.cu, ops_f32.cu,
+ *      seqmix.cu).  No reference equivalents: the reference's inference path is the Qwen3 block only.  "act_f32" / "*_f32" flags select the
+ *      activation type that feeds matmuls and fills caches: 0 = bf16 bits, 1 = float (a model run entirely in 32-bit). ---- */
+int kf_embed_f32(kf_ctx* ctx, float* out_dev, const kf_tensor_desc* w, const int32_t* tokens_dev, int M);
+/* y[M][ldy] (float) = x[M][ldx] . W^T for a bf16 weight of ANY shape; shapes the tuned kernels take are forwarded to kf_linear */
+int kf_linear_g(kf_ctx* ctx, float* y_dev, int ldy, const kf_tensor_desc* w, const void* x_dev, int act_f32, int ldx, int M);
+int kf_linear_g_swiglu(kf_ctx* ctx, void* y_dev, int ldy, const kf_tensor_desc* w_gate, const kf_tensor_desc* w_up, const void* x_dev, int act_f32,
+                       int ldx, int M);
+int kf_linear_grouped(kf_ctx* ctx, void* y_dev, int ldy, const void* const* w_table_dev, const void* const* w2_table_dev, int n_groups, int N, int K,
+                      const void* x_dev, int act_f32, int ldx, const int32_t* offsets_dev, const int32_t* slot_group_dev, const int32_t* src_row_dev,
+                      int slots);
+/* RMS norm in `groups` equal consecutive parts of a float row, times a bf16 weight; optional gate on the input (1: sigmoid(gate + bias),
+ * 2: silu(gate)); out_kind 0 / 1: bf16 / float rows, 2: res += mult * result */
+int kf_group_rmsnorm(kf_ctx* ctx, void* out_dev, int out_kind, int ldo, float* res_dev, float mult, const float* x_dev, int ldx, const float* gate_dev,
+                     int ldg, const void* gate_bias_bf16_dev, int gate_kind, const void* w_bf16_dev, const int32_t* row_idx_dev, int rows, int dim,
+                     int groups, float eps);
+int kf_f32_to_bf16(kf_ctx* ctx, void* out_bf16_dev, const float* in_dev, size_t n);
+int kf_moe_route(kf_ctx* ctx, int32_t* idx_dev, float* wgt_dev, int32_t* offsets_dev, int32_t* entry_slot_dev, int32_t* slot_row_dev,
+                 int32_t* slot_group_dev, int32_t* work_dev, const float* logits_dev, int ldl, const void* bias_bf16_dev, int M, int E, int top);
+int kf_moe_combine(kf_ctx* ctx, float* out_dev, const float* y_slots_dev, const int32_t* entry_slot_dev, const float* wgt_dev, const float* shared_dev,
+                   const float* shared_gate_logit_dev, int M, int dim, int top);
+int kf_conv_silu(kf_ctx* ctx, float* xbc_out_dev, const float* u_dev, int ldu, int c0, const void* w_bf16_dev, const void* b_bf16_dev, float* tail_dev,
+                 size_t tail_stride, const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int C, int K);
+int kf_ssm_scan(kf_ctx* ctx, float* y_dev, int ldy, const float* xbc_dev, const float* u_dev, int ldu, int dt_off, const void* dt_bias_bf16_dev,
+                const void* A_log_bf16_dev, const void* D_bf16_dev, float* state_dev, size_t state_stride, const int32_t* pos_dev,
+                const int32_t* slot_dev, int nseq, int T, int H, int P, int N, int G);
+int kf_latent_append(kf_ctx* ctx, void* cache_dev, int cache_f32, size_t slot_stride, const float* ckr_dev, int ldc, const void* norm_w_bf16_dev,
+                     const float* inv_freq_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int rank, int rot_dim, int rot_dims, float eps);
+int kf_latent_attention(kf_ctx* ctx, float* lat_out_dev, float* qa_work_dev, const float* q_dev, int ldq, const void* w_uk_bf16_dev,
+                        const void* sink_bf16_dev, const void* cache_dev, int cache_f32, size_t slot_stride, const float* inv_freq_dev,
+                        const int32_t* pos_dev, const int32_t* slot_dev, int M, int H, int dn, int rot_dim, int rot_dims, int rank, float scale);
+int kf_latent_expand(kf_ctx* ctx, void* out_dev, int out_f32, const float* lat_dev, const void* w_uv_bf16_dev, const float* gate_logit_dev, int ldg,
+                     int M, int H, int dv, int rank);
+
 #ifdef __cplusplus
 }
 #endif

@@ -71,6 +71,14 @@ void* kf_model_vcache(kf_model* m, int layer);
  * Synchronous: returns after the results are in host memory. */
 int kf_model_forward(kf_model* m, const int32_t* tokens_host, const int32_t* pos_host, int M, int seq_mode, void* logits_host,
                      int32_t* next_host);
+/* The same step for architectures with a sequence-slot cache / state manager (hybrid stacks): the tokens of modes 0 / 2 belong to sequence
+ * slot `slot` (mode 1: token m to slot m); sel (optional, int32[n_sel], indices into the M tokens) chooses the rows whose logits are formed
+ * (n_sel <= gpt.logit_rows); logits_f32_host (optional) receives them as float [rows][vocab].  A slot needs no clearing: a sequence starts
+ * at position 0.  kf_model_slot_acquire / _release hand slots out and take them back (gpt.max_batch of them). */
+int kf_model_forward_ex(kf_model* m, const int32_t* tokens_host, const int32_t* pos_host, int M, int seq_mode, int slot, const int32_t* sel_host,
+                        int n_sel, void* logits_bf16_host, float* logits_f32_host, int32_t* next_host);
+int kf_model_slot_acquire(kf_model* m, int* slot_out);
+int kf_model_slot_release(kf_model* m, int slot);
 /* n_steps greedy decode steps entirely on the device (each step a CUDA-graph replay feeding its argmax back as the next token),
  * continuing from the tokens/positions of the last kf_model_forward.  Asynchronous; kf_ctx_sync() to wait. */
 int kf_model_decode_loop(kf_model* m, int n_steps, int M);

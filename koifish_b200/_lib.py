@@ -98,6 +98,19 @@ SIGNATURES = {
     "kf_linear_axb": (_I, [_P, _P, _P, _P, _I, C.c_float, C.c_float, _P]),
     "kf_argmax": (_I, [_P, _P, _P, _I, _I]),
     "kf_sample": (_I, [_P, _P, _P, _I, _I, C.c_float, _I, C.c_float, _P, _I]),
+    "kf_embed_f32": (_I, [_P, _P, _DESCP, _P, _I]),
+    "kf_linear_g": (_I, [_P, _P, _I, _DESCP, _P, _I, _I, _I]),
+    "kf_linear_g_swiglu": (_I, [_P, _P, _I, _DESCP, _DESCP, _P, _I, _I, _I]),
+    "kf_linear_grouped": (_I, [_P, _P, _I, _P, _P, _I, _I, _I, _P, _I, _I, _P, _P, _P, _I]),
+    "kf_group_rmsnorm": (_I, [_P, _P, _I, _I, _P, _F, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _I, _F]),
+    "kf_f32_to_bf16": (_I, [_P, _P, _P, _SZ]),
+    "kf_moe_route": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I]),
+    "kf_moe_combine": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I]),
+    "kf_conv_silu": (_I, [_P, _P, _P, _I, _I, _P, _P, _P, _SZ, _P, _P, _I, _I, _I, _I]),
+    "kf_ssm_scan": (_I, [_P, _P, _I, _P, _P, _I, _I, _P, _P, _P, _P, _SZ, _P, _P, _I, _I, _I, _I, _I, _I]),
+    "kf_latent_append": (_I, [_P, _P, _I, _SZ, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F]),
+    "kf_latent_attention": (_I, [_P, _P, _P, _P, _I, _P, _P, _P, _I, _SZ, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F]),
+    "kf_latent_expand": (_I, [_P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I]),
     "kf_nccl_unique_id": (_I, [_P]),
     "kf_ctx_init_nccl": (_I, [_P, _P, _I, _I]),
     "kf_allreduce_bf16": (_I, [_P, _P, _SZ]),
@@ -118,6 +131,9 @@ SIGNATURES = {
     "kf_model_kcache": (_P, [_P, _I]),
     "kf_model_vcache": (_P, [_P, _I]),
     "kf_model_forward": (_I, [_P, _P, _P, _I, _I, _P, _P]),
+    "kf_model_forward_ex": (_I, [_P, _P, _P, _I, _I, _I, _P, _I, _P, _P, _P]),
+    "kf_model_slot_acquire": (_I, [_P, C.POINTER(_I)]),
+    "kf_model_slot_release": (_I, [_P, _I]),
     "kf_model_decode_loop": (_I, [_P, _I, _I]),
     "kf_model_read_state": (_I, [_P, _P, _P, _I]),
     "kf_model_save": (_I, [_P, C.c_char_p]),

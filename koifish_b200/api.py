@@ -455,6 +455,39 @@ class Model:
                                               logits.ctypes.data if want_logits else None, nxt.ctypes.data if want_next else None), "kf_model_forward")
         return logits, nxt
 
+    def forward_rows(self, tokens, pos0, slot=0, rows=None, want_next=False):
+        """One step of consecutive tokens of the sequence in `slot` (architectures with a slot cache / state manager): positions pos0 ..,
+        fp32 logits [len(rows), vocab] of the chosen rows (indices into `tokens`; None: no logits), optionally their sampled tokens."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32).reshape(-1)
+        pos = np.arange(pos0, pos0 + tokens.size, dtype=np.int32)
+        sel = np.ascontiguousarray(rows, dtype=np.int32).reshape(-1) if rows is not None and len(rows) else None
+        R = sel.size if sel is not None else 0
+        logits = np.empty((R, self.info.vocab), dtype=np.float32) if R else None
+        nxt = np.empty(R, dtype=np.int32) if (want_next and R) else None
+        self._check(self.lib.kf_model_forward_ex(self.h, tokens.ctypes.data, pos.ctypes.data, tokens.size, 0, int(slot),
+                                                 sel.ctypes.data if R else None, R, None, logits.ctypes.data if R else None,
+                                                 nxt.ctypes.data if nxt is not None else None), "kf_model_forward_ex")
+        return logits, nxt
+
+    def forward_batch(self, tokens, pos, want_next=False):
+        """One token for each of M sequences (slots 0 .. M-1) -> fp32 logits [M, vocab] (architectures with fp32 logits)."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32).reshape(-1)
+        pos = np.ascontiguousarray(pos, dtype=np.int32).reshape(-1)
+        M = tokens.size
+        logits = np.empty((M, self.info.vocab), dtype=np.float32)
+        nxt = np.empty(M, dtype=np.int32) if want_next else None
+        self._check(self.lib.kf_model_forward_ex(self.h, tokens.ctypes.data, pos.ctypes.data, M, 1, 0, None, 0, None, logits.ctypes.data,
+                                                 nxt.ctypes.data if want_next else None), "kf_model_forward_ex")
+        return logits, nxt
+
+    def acquire_slot(self):
+        s = C.c_int(-1)
+        self._check(self.lib.kf_model_slot_acquire(self.h, C.byref(s)), "kf_model_slot_acquire")
+        return int(s.value)
+
+    def release_slot(self, slot):
+        self._check(self.lib.kf_model_slot_release(self.h, int(slot)), "kf_model_slot_release")
+
     def prefill(self, tokens, pos0=0, want_logits=False):
         """run a prompt through in panels of info.max_tokens; returns (logits of the last token or None, greedy next token).  Leaves
         the model ready for decode_loop(n, 1)."""
@@ -736,7 +769,7 @@ def kun_write(path, config, tensors):
         raise KoifishError(st, "kf_kun_write", _take_string(lib, err) if err.value else "")
 
 
-def from_pretrained(ctx, model_dir, quantizer=None, max_seq_len=1024, max_batch=1, tp_rank=0, tp_world=1):
+def from_pretrained(ctx, model_dir, quantizer=None, max_seq_len=1024, max_batch=1, tp_rank=0, tp_world=1, gpt=None):
     """the reference's `--hf <dir>` path (MODEL_CARD::InitHugFace, src/Utils/CLI_params.cpp:2224-2300 + Fish::LoadFolderOfST): an HF checkpoint
     directory (config.json, *.safetensors, tokenizer.json) -> (Model with every tensor loaded, Tokenizer).  `quantizer`: a Koifish "quantizer"
     block to quantise a bf16 checkpoint at load; a vendor-quantised (AWQ) checkpoint brings its own through config.json's quantization_config."""
@@ -744,6 +777,7 @@ def from_pretrained(ctx, model_dir, quantizer=None, max_seq_len=1024, max_batch=
     with open(os.path.join(str(model_dir), "config.json")) as f:
         hf = json.load(f)
     cfg = {"hf_config": hf, "gpt": {"max_seq_len": int(max_seq_len), "max_batch": int(max_batch)}}
+    cfg["gpt"].update(gpt or {})  # e.g. max_prefill, logit_rows, compute_dtype
     if quantizer:
         cfg["quantizer"] = quantizer
     model = Model(ctx, cfg, tp_rank, tp_world)
@@ -751,4 +785,5 @@ def from_pretrained(ctx, model_dir, quantizer=None, max_seq_len=1024, max_batch=
     missing = len(model.tensor_names()) - loaded
     if missing:
         raise KoifishError(L.KF_ERR_BAD_ARG, "from_pretrained", "%d of the model's tensors are not in '%s'" % (missing, model_dir))
-    return model, Tokenizer(model_dir)
+    has_tok = os.path.exists(os.path.join(str(model_dir), "tokenizer.json"))
+    return model, (Tokenizer(model_dir) if has_tok else None)

@@ -1,0 +1,283 @@
+// linear_g.cu -- matmuls of ANY shape over bf16 weights with fp32 results, for the layers whose sizes the tuned kernels of gemv.cu /
+// gemm_tc.cu do not take (their K must be a multiple of 128 and their N of 16): y[m][n] = sum_k x[m][k] * W[n][k].
+//   * activations x are bf16 bits (act_f32 = 0: the products are exact in fp32 and accumulate in fp32, i.e. the arithmetic of a bf16
+//     tensor-core matmul) or float (act_f32 = 1: a true 32-bit matmul, FMA by FMA, no reduced-precision mode);
+//   * "grouped" form for mixtures of experts: every output row (a slot) names the weight matrix it uses; slots of one expert are
+//     contiguous (offsets[e] .. offsets[e+1]) and may gather their input row through src_row;
+//   * DUAL form: two weight tables A, B of equal shape and y = silu(A x) * (B x), the gate / up pair of a gated feed-forward.
+// Two kernels: a warp-per-output GEMV for a handful of rows (decode: every weight row is read once, 16-byte loads when the row length
+// allows) and a 64 x 64 x 16 shared-memory tile kernel for panels (mma.sync m16n8k16 for bf16 activations, FFMA for float ones).
+// No reference equivalent: the reference's SLP::Forw hands every shape to cuBLASLt (src/Device/CUDA/NeuronFuse.cu:305-381).
+#include "kf_common.cuh"
+
+namespace {
+
+struct LinArgs {
+    const uint16_t* W0;          // single weight (dense) -- or
+    const uint16_t* const* Wt0;  // table of per-expert weights (grouped)
+    const uint16_t* W1;          // DUAL: second weight
+    const uint16_t* const* Wt1;
+    const void* x;               // [rows][ldx] bf16 bits or float
+    void* y;                     // [slots][ldy] float (or, DUAL with out_act, the activation type)
+    const int32_t* offsets;      // grouped: [E + 1] slot ranges; nullptr: one group [0, M)
+    const int32_t* src_row;      // slot -> row of x; nullptr: slot
+    const int32_t* slot_group;   // GEMV form: slot -> expert; nullptr: 0
+    int M, N, K, ldx, ldy;
+    int out_act;                 // DUAL only: 0 = float out, 1 = bf16 out, (float activations: float out)
+};
+
+template <typename TA>
+__device__ __forceinline__ float ld_act(const TA* p);
+template <>
+__device__ __forceinline__ float ld_act<uint16_t>(const uint16_t* p) { return bf16_bits_to_f32(*p); }
+template <>
+__device__ __forceinline__ float ld_act<float>(const float* p) { return *p; }
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+
+// ------------------------------------------------------------------------------------------------------------------ GEMV (few slots)
+// one warp per (slot, output n): lanes stride over k, fixed butterfly reduction -> deterministic.
+template <typename TA, bool DUAL>
+__global__ void __launch_bounds__(256) kf_lin_gemv_kernel(LinArgs a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n    = blockIdx.x * 8 + warp;
+    const int slot = blockIdx.y;
+    if (n >= a.N) return;
+    const int g   = a.slot_group ? a.slot_group[slot] : 0;
+    const int row = a.src_row ? a.src_row[slot] : slot;
+    const uint16_t* w0 = (a.Wt0 ? a.Wt0[g] : a.W0) + (size_t)n * a.K;
+    const uint16_t* w1 = DUAL ? (a.Wt1 ? a.Wt1[g] : a.W1) + (size_t)n * a.K : nullptr;
+    const TA* x = (const TA*)a.x + (size_t)row * a.ldx;
+    float s0 = 0.f, s1 = 0.f;
+    const bool vec = (a.K % 8 == 0) && (a.ldx % 8 == 0) && (((uintptr_t)w0 & 15) == 0) && (((uintptr_t)x & 15) == 0) && (!DUAL || ((uintptr_t)w1 & 15) == 0);
+    if (vec) {
+        for (int k = lane * 8; k < a.K; k += 256) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(w0 + k);
+            const uint32_t wq[4] = {wv.x, wv.y, wv.z, wv.w};
+            float xv[8];
+            if (sizeof(TA) == 2) {
+                const uint4 xq4 = *reinterpret_cast<const uint4*>((const uint16_t*)x + k);
+                const uint32_t xq[4] = {xq4.x, xq4.y, xq4.z, xq4.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) xv[2 * j] = bf16lo(xq[j]), xv[2 * j + 1] = bf16hi(xq[j]);
+            } else {
+                const float4 f0 = *reinterpret_cast<const float4*>((const float*)x + k), f1 = *reinterpret_cast<const float4*>((const float*)x + k + 4);
+                xv[0] = f0.x, xv[1] = f0.y, xv[2] = f0.z, xv[3] = f0.w, xv[4] = f1.x, xv[5] = f1.y, xv[6] = f1.z, xv[7] = f1.w;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) s0 = fmaf(bf16lo(wq[j]), xv[2 * j], s0), s0 = fmaf(bf16hi(wq[j]), xv[2 * j + 1], s0);
+            if (DUAL) {
+                const uint4 uv = *reinterpret_cast<const uint4*>(w1 + k);
+                const uint32_t uq[4] = {uv.x, uv.y, uv.z, uv.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) s1 = fmaf(bf16lo(uq[j]), xv[2 * j], s1), s1 = fmaf(bf16hi(uq[j]), xv[2 * j + 1], s1);
+            }
+        }
+    } else {
+        for (int k = lane; k < a.K; k += 32) {
+            const float xv = ld_act<TA>(x + k);
+            s0 = fmaf(bf16_bits_to_f32(w0[k]), xv, s0);
+            if (DUAL) s1 = fmaf(bf16_bits_to_f32(w1[k]), xv, s1);
+        }
+    }
+    s0 = warp_sum(s0);
+    if (DUAL) s1 = warp_sum(s1);
+    if (lane == 0) {
+        const float r = DUAL ? silu_f(s0) * s1 : s0;
+        if (DUAL && a.out_act == 1)
+            ((uint16_t*)a.y)[(size_t)slot * a.ldy + n] = f32_to_bf16_bits(r);
+        else
+            ((float*)a.y)[(size_t)slot * a.ldy + n] = r;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------------ tile kernel
+// 64 slots x 64 outputs per CTA, k in steps of 16; 256 threads.  Float activations: each thread a 4 x 4 block of FFMA accumulators.
+// bf16 activations: 8 warps as 4 (m) x 2 (n), each warp 16 x 32 through four mma.sync.m16n8k16 per k step; operands converted from the
+// same shared tiles.  Every load is bounds-checked, so M, N and K are free.
+constexpr int BM = 64, BN = 64, BK = 16;
+
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, const uint32_t* b) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <typename TA, bool DUAL>
+__global__ void __launch_bounds__(256) kf_lin_tile_kernel(LinArgs a) {
+    const int g    = blockIdx.z;
+    const int lo   = a.offsets ? a.offsets[g] : 0;
+    const int hi   = a.offsets ? a.offsets[g + 1] : a.M;
+    const int m0   = lo + blockIdx.y * BM;
+    if (m0 >= hi) return;
+    const int n0 = blockIdx.x * BN;
+    const uint16_t* W0 = a.Wt0 ? a.Wt0[g] : a.W0;
+    const uint16_t* W1 = DUAL ? (a.Wt1 ? a.Wt1[g] : a.W1) : nullptr;
+    constexpr bool MMA = sizeof(TA) == 2;
+    // shared tiles, k-major rows padded against bank conflicts
+    __shared__ TA sx[BM][BK + (MMA ? 8 : 1)];
+    __shared__ uint16_t sw0[BN][BK + 8];
+    __shared__ uint16_t sw1[DUAL ? BN : 1][BK + 8];
+    __shared__ int srow[BM];
+    const int tid = threadIdx.x;
+    if (tid < BM) {
+        const int s = m0 + tid;
+        srow[tid]   = s < hi ? (a.src_row ? a.src_row[s] : s) : -1;
+    }
+    __syncthreads();
+    float acc0[16], acc1[DUAL ? 16 : 1];
+#pragma unroll
+    for (int i = 0; i < 16; i++) acc0[i] = 0.f;
+    if (DUAL)
+#pragma unroll
+        for (int i = 0; i < 16; i++) acc1[i] = 0.f;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int wm = warp & 3, wn = warp >> 2;      // MMA: warp tile rows wm*16, cols wn*32
+    const int tr = tid >> 4, tc = tid & 15;        // FFMA: thread rows tr*4.., cols tc*4..
+    for (int k0 = 0; k0 < a.K; k0 += BK) {
+        // stage x: 64 x 16 elements, 4 per thread
+        {
+            const int r = tid >> 2, c = (tid & 3) * 4;
+            const int row = srow[r];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int k = k0 + c + j;
+                TA v = TA(0);
+                if (row >= 0 && k < a.K) v = ((const TA*)a.x)[(size_t)row * a.ldx + k];
+                sx[r][c + j] = v;
+            }
+            const int n = n0 + r;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int k = k0 + c + j;
+                const bool ok = n < a.N && k < a.K;
+                sw0[r][c + j] = ok ? W0[(size_t)n * a.K + k] : (uint16_t)0;
+                if (DUAL) sw1[r][c + j] = ok ? W1[(size_t)n * a.K + k] : (uint16_t)0;
+            }
+        }
+        __syncthreads();
+        if (MMA) {
+            const int gr = lane >> 2, tg = lane & 3;
+            uint32_t af[4];
+            const uint16_t* xa = (const uint16_t*)&sx[wm * 16][0];
+            const int ldsx = BK + 8;
+            af[0] = *reinterpret_cast<const uint32_t*>(xa + (gr)*ldsx + tg * 2);
+            af[1] = *reinterpret_cast<const uint32_t*>(xa + (gr + 8) * ldsx + tg * 2);
+            af[2] = *reinterpret_cast<const uint32_t*>(xa + (gr)*ldsx + tg * 2 + 8);
+            af[3] = *reinterpret_cast<const uint32_t*>(xa + (gr + 8) * ldsx + tg * 2 + 8);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int nr = wn * 32 + j * 8 + gr;
+                uint32_t bf[2];
+                bf[0] = *reinterpret_cast<const uint32_t*>(&sw0[nr][tg * 2]);
+                bf[1] = *reinterpret_cast<const uint32_t*>(&sw0[nr][tg * 2 + 8]);
+                mma_bf16_16816(&acc0[j * 4], af, bf);
+                if (DUAL) {
+                    bf[0] = *reinterpret_cast<const uint32_t*>(&sw1[nr][tg * 2]);
+                    bf[1] = *reinterpret_cast<const uint32_t*>(&sw1[nr][tg * 2 + 8]);
+                    mma_bf16_16816(&acc1[j * 4], af, bf);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < BK; k++) {
+                float xv[4], wv[4], uv[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) xv[i] = ld_act<TA>(&sx[tr * 4 + i][k]);
+#pragma unroll
+                for (int j = 0; j < 4; j++) wv[j] = bf16_bits_to_f32(sw0[tc * 4 + j][k]);
+                if (DUAL)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) uv[j] = bf16_bits_to_f32(sw1[tc * 4 + j][k]);
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        acc0[i * 4 + j] = fmaf(xv[i], wv[j], acc0[i * 4 + j]);
+                        if (DUAL) acc1[i * 4 + j] = fmaf(xv[i], uv[j], acc1[i * 4 + j]);
+                    }
+            }
+        }
+        __syncthreads();
+    }
+    auto store = [&](int r, int n, float v0, float v1) {
+        const int s = m0 + r;
+        if (s >= hi || n >= a.N) return;
+        const float v = DUAL ? silu_f(v0) * v1 : v0;
+        if (DUAL && a.out_act == 1)
+            ((uint16_t*)a.y)[(size_t)s * a.ldy + n] = f32_to_bf16_bits(v);
+        else
+            ((float*)a.y)[(size_t)s * a.ldy + n] = v;
+    };
+    if (MMA) {
+        const int gr = lane >> 2, tg = lane & 3;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + wn * 32 + j * 8 + tg * 2, r = wm * 16 + gr;
+            store(r, n, acc0[j * 4 + 0], DUAL ? acc1[j * 4 + 0] : 0.f);
+            store(r, n + 1, acc0[j * 4 + 1], DUAL ? acc1[j * 4 + 1] : 0.f);
+            store(r + 8, n, acc0[j * 4 + 2], DUAL ? acc1[j * 4 + 2] : 0.f);
+            store(r + 8, n + 1, acc0[j * 4 + 3], DUAL ? acc1[j * 4 + 3] : 0.f);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) store(tr * 4 + i, n0 + tc * 4 + j, acc0[i * 4 + j], DUAL ? acc1[i * 4 + j] : 0.f);
+    }
+}
+
+template <typename TA, bool DUAL>
+int launch(kf_ctx* ctx, const LinArgs& a, int slots, int groups, bool gemv) {
+    if (gemv) {
+        dim3 grid((a.N + 7) / 8, slots);
+        kf_lin_gemv_kernel<TA, DUAL><<<grid, 256, 0, ctx->stream>>>(a);
+    } else {
+        dim3 grid((a.N + BN - 1) / BN, (slots + BM - 1) / BM, groups);
+        kf_lin_tile_kernel<TA, DUAL><<<grid, 256, 0, ctx->stream>>>(a);
+    }
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+int dispatch(kf_ctx* ctx, const LinArgs& a, int slots, int groups, bool gemv, bool dual, int act_f32) {
+    if (act_f32) return dual ? launch<float, true>(ctx, a, slots, groups, gemv) : launch<float, false>(ctx, a, slots, groups, gemv);
+    return dual ? launch<uint16_t, true>(ctx, a, slots, groups, gemv) : launch<uint16_t, false>(ctx, a, slots, groups, gemv);
+}
+constexpr int kGemvMaxSlots = 16;
+}  // namespace
+
+extern "C" int kf_linear_g(kf_ctx* ctx, float* y, int ldy, const kf_tensor_desc* w, const void* x, int act_f32, int ldx, int M) {
+    if (!ctx || !y || !w || !x) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, w->type == KF_T_BF16 && M >= 1 && w->rows >= 1 && w->cols >= 1 && ldx >= w->cols && ldy >= w->rows, "bf16 weight, ld >= extent");
+    // shapes the tuned kernels take go there (tcgen05 / TMEM panels, the HBM-rate GEMV); fp32 result through their fp32 epilogue
+    if (!act_f32 && ldx == w->cols && ldy == w->rows && w->cols % 128 == 0 && w->rows % 16 == 0 && w->rows >= 16 && ctx->tc_min_m != 0 &&
+        (((uintptr_t)w->data_dev | (uintptr_t)x | (uintptr_t)y) & 15) == 0)
+        return kf_linear(ctx, y, w, x, M, KF_EPI_F32, nullptr);
+    LinArgs a = {};
+    a.W0 = (const uint16_t*)w->data_dev, a.x = x, a.y = y, a.M = M, a.N = w->rows, a.K = w->cols, a.ldx = ldx, a.ldy = ldy;
+    return dispatch(ctx, a, M, 1, M <= kGemvMaxSlots, false, act_f32);
+}
+// y = silu(Wg x) * (Wu x), written in the activation type (bf16 bits, or float when act_f32)
+extern "C" int kf_linear_g_swiglu(kf_ctx* ctx, void* y, int ldy, const kf_tensor_desc* wg, const kf_tensor_desc* wu, const void* x, int act_f32,
+                                  int ldx, int M) {
+    if (!ctx || !y || !wg || !wu || !x) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, wg->type == KF_T_BF16 && wu->type == KF_T_BF16 && wg->rows == wu->rows && wg->cols == wu->cols && M >= 1 && ldx >= wg->cols &&
+                        ldy >= wg->rows, "gate / up: bf16, equal shapes");
+    LinArgs a = {};
+    a.W0 = (const uint16_t*)wg->data_dev, a.W1 = (const uint16_t*)wu->data_dev, a.x = x, a.y = y, a.M = M, a.N = wg->rows, a.K = wg->cols;
+    a.ldx = ldx, a.ldy = ldy, a.out_act = act_f32 ? 0 : 1;
+    return dispatch(ctx, a, M, 1, M <= kGemvMaxSlots, true, act_f32);
+}
+// Grouped matmul over expert-sorted slots.  w_table / w2_table: device arrays of n_groups bf16 weight pointers ([N][K] each);
+// offsets: device int32 [n_groups + 1]; slot_group: device int32 [slots] (the expert of each slot); src_row: device int32 [slots] or
+// NULL.  w2_table != NULL: y = silu(W x) * (W2 x) in the activation type; else y is float.  `slots` is the launch bound (tokens x top).
+extern "C" int kf_linear_grouped(kf_ctx* ctx, void* y, int ldy, const void* const* w_table, const void* const* w2_table, int n_groups, int N, int K,
+                                 const void* x, int act_f32, int ldx, const int32_t* offsets, const int32_t* slot_group, const int32_t* src_row,
+                                 int slots) {
+    if (!ctx || !y || !w_table || !x || !offsets || !slot_group) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, n_groups >= 1 && N >= 1 && K >= 1 && slots >= 1 && ldx >= K && ldy >= N, "shape");
+    LinArgs a = {};
+    a.Wt0 = (const uint16_t* const*)w_table, a.Wt1 = (const uint16_t* const*)w2_table, a.x = x, a.y = y, a.M = slots, a.N = N, a.K = K;
+    a.ldx = ldx, a.ldy = ldy, a.offsets = offsets, a.slot_group = slot_group, a.src_row = src_row, a.out_act = act_f32 ? 0 : 1;
+    return dispatch(ctx, a, slots, n_groups, slots <= kGemvMaxSlots, w2_table != nullptr, act_f32);
+}

@@ -1,0 +1,225 @@
+// ops_f32.cu -- the small ops of models whose residual stream, norms and routers are kept in 32-bit floats: embedding rows widened to
+// fp32, grouped RMS norm (optionally of a gated input, optionally accumulated into the residual), and the router / dispatch / combine
+// steps of a mixture of experts.  Outputs that feed a matmul are written in the activation type: bf16 bits, or float for a model that
+// runs entirely in 32-bit.  No reference equivalent (the reference's norms are CU_rms_infer over bf16 rows, layernorm.cuh:801-859, and
+// it has no expert routing on the inference path).
+#include <math.h>
+
+#include "kf_common.cuh"
+
+namespace {
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+
+__global__ void kf_embed_f32_kernel(float* __restrict__ out, const uint16_t* __restrict__ table, const int32_t* __restrict__ tokens, int dim) {
+    const uint16_t* row = table + (size_t)tokens[blockIdx.x] * dim;
+    float* o            = out + (size_t)blockIdx.x * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = bf16_bits_to_f32(row[i]);
+}
+
+// One block per (row, group).  v = x * gatefn(g) (GATE 0: none, 1: sigmoid(g + gate_bias), 2: silu(g));  r = v / sqrt(mean_group(v^2) + eps) * w;
+// ACC: res[row] += mult * r (fp32 residual stream)  else  out[row] = r in the activation type.
+template <int GATE, bool ACC, typename TO>
+__global__ void __launch_bounds__(256) kf_group_norm_kernel(TO* __restrict__ out, int ldo, float* __restrict__ res, const float* __restrict__ x, int ldx,
+                                                            const float* __restrict__ gate, int ldg, const uint16_t* __restrict__ gate_bias,
+                                                            const uint16_t* __restrict__ w, const int32_t* __restrict__ row_idx, int dim, int groups,
+                                                            float eps, float mult) {
+    __shared__ float red[32];
+    const int r = blockIdx.x, grp = blockIdx.y, gs = dim / groups;
+    const int src = row_idx ? row_idx[r] : r;
+    const float* xr = x + (size_t)src * ldx + grp * gs;
+    const float* gr = GATE ? gate + (size_t)src * ldg + grp * gs : nullptr;
+    auto val = [&](int i) -> float {
+        float v = xr[i];
+        if (GATE == 1) v *= sigmoid_f(gr[i] + (gate_bias ? bf16_bits_to_f32(gate_bias[grp * gs + i]) : 0.f));
+        if (GATE == 2) {
+            const float z = gr[i];
+            v *= z * sigmoid_f(z);
+        }
+        return v;
+    };
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+        const float v = val(i);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float s = 1.0f / sqrtf(ss / (float)gs + eps);
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+        const float o = val(i) * s * bf16_bits_to_f32(w[grp * gs + i]);
+        if (ACC) {
+            float* p = res + (size_t)r * dim + grp * gs + i;
+            *p       = *p + mult * o;
+        } else if (sizeof(TO) == 2) {
+            ((uint16_t*)out)[(size_t)r * ldo + grp * gs + i] = f32_to_bf16_bits(o);
+        } else {
+            ((float*)out)[(size_t)r * ldo + grp * gs + i] = o;
+        }
+    }
+}
+
+__global__ void kf_f32_to_bf16_kernel(uint16_t* __restrict__ out, const float* __restrict__ in, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = f32_to_bf16_bits(in[i]);
+}
+
+// ---- mixture of experts ---------------------------------------------------------------------------------------------------
+// one warp per token: `top` rounds of arg-max over the E router logits (+ bias), ties to the lower index; weights = softmax over the
+// chosen logits only.  All in fp32.
+__global__ void __launch_bounds__(128) kf_moe_route_kernel(int32_t* __restrict__ idx, float* __restrict__ wgt, const float* __restrict__ logits, int ldl,
+                                                           const uint16_t* __restrict__ bias, int M, int E, int top) {
+    const int m = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (m >= M) return;
+    const float* lg = logits + (size_t)m * ldl;
+    float first = 0.f, den = 0.f;
+    for (int j = 0; j < top; j++) {
+        float best = -INFINITY;
+        int bi     = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            bool taken = false;
+            for (int q = 0; q < j; q++) taken = taken || idx[(size_t)m * top + q] == e;
+            if (taken) continue;
+            const float v = lg[e] + (bias ? bf16_bits_to_f32(bias[e]) : 0.f);
+            if (v > best || (v == best && e < bi)) best = v, bi = e;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi   = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) best = ob, bi = oi;
+        }
+        if (j == 0) first = best;
+        const float p = expf(best - first);
+        den += p;
+        if (lane == 0) idx[(size_t)m * top + j] = bi, wgt[(size_t)m * top + j] = p;
+        __syncwarp();
+    }
+    if (lane < top) {
+        for (int j = lane; j < top; j += 32) wgt[(size_t)m * top + j] /= den;
+    }
+}
+// one block per expert: the entries (token, choice) routed to it, ranked in entry order (ballot + popc compaction)
+__global__ void __launch_bounds__(256) kf_moe_rank_kernel(int32_t* __restrict__ rank, int32_t* __restrict__ count, const int32_t* __restrict__ idx, int n) {
+    __shared__ int wsum[8];
+    __shared__ int base;
+    const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) base = 0;
+    __syncthreads();
+    for (int i0 = 0; i0 < n; i0 += 256) {
+        const int i    = i0 + threadIdx.x;
+        const bool hit = i < n && idx[i] == e;
+        const unsigned b = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0) wsum[warp] = __popc(b);
+        __syncthreads();
+        int before = base;
+        for (int q = 0; q < warp; q++) before += wsum[q];
+        if (hit) rank[i] = before + __popc(b & ((1u << lane) - 1));
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int t = 0;
+            for (int q = 0; q < 8; q++) t += wsum[q];
+            base += t;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) count[e] = base;
+}
+// offsets = exclusive scan of the counts (one thread: E is small); then each entry learns its slot
+__global__ void kf_moe_offsets_kernel(int32_t* __restrict__ offsets, const int32_t* __restrict__ count, int E) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        int s = 0;
+        for (int e = 0; e < E; e++) offsets[e] = s, s += count[e];
+        offsets[E] = s;
+    }
+}
+__global__ void kf_moe_slots_kernel(int32_t* __restrict__ entry_slot, int32_t* __restrict__ slot_row, int32_t* __restrict__ slot_group,
+                                    const int32_t* __restrict__ idx, const int32_t* __restrict__ rank, const int32_t* __restrict__ offsets, int n, int top) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int e = idx[i], s = offsets[e] + rank[i];
+    entry_slot[i] = s, slot_row[s] = i / top, slot_group[s] = e;
+}
+// out[m] = sum_j wgt[m][j] * y[slot(m, j)]  (+ sigmoid(sg[m]) * shared[m]), choices added in their routing order
+__global__ void kf_moe_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const int32_t* __restrict__ entry_slot,
+                                      const float* __restrict__ wgt, const float* __restrict__ shared, const float* __restrict__ sg, int dim, int top) {
+    const int m = blockIdx.x;
+    const float gate = shared ? (sg ? sigmoid_f(sg[m]) : 1.f) : 0.f;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float s = 0.f;
+        for (int j = 0; j < top; j++) s = fmaf(wgt[(size_t)m * top + j], y[(size_t)entry_slot[(size_t)m * top + j] * dim + d], s);
+        if (shared) s = fmaf(gate, shared[(size_t)m * dim + d], s);
+        out[(size_t)m * dim + d] = s;
+    }
+}
+}  // namespace
+
+extern "C" int kf_embed_f32(kf_ctx* ctx, float* out, const kf_tensor_desc* w, const int32_t* tokens_dev, int M) {
+    if (!ctx || !out || !w || !tokens_dev) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, w->type == KF_T_BF16 && M >= 1, "bf16 table");
+    kf_embed_f32_kernel<<<M, 256, 0, ctx->stream>>>(out, (const uint16_t*)w->data_dev, tokens_dev, w->cols);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+
+// gate_kind 0: none; 1: x * sigmoid(gate + gate_bias); 2: x * silu(gate).  out_kind 0: bf16 bits [rows][ldo]; 1: float [rows][ldo];
+// 2: res[rows][dim] += mult * result (out is ignored).  row_idx (device, optional): source row of each output row.
+extern "C" int kf_group_rmsnorm(kf_ctx* ctx, void* out, int out_kind, int ldo, float* res, float mult, const float* x, int ldx, const float* gate, int ldg,
+                                const void* gate_bias_bf16, int gate_kind, const void* w_bf16, const int32_t* row_idx, int rows, int dim, int groups,
+                                float eps) {
+    if (!ctx || !x || !w_bf16) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, rows >= 1 && dim >= 1 && groups >= 1 && dim % groups == 0, "groups must divide dim");
+    KF_REQUIRE(ctx, gate_kind >= 0 && gate_kind <= 2 && (gate_kind == 0 || gate) && out_kind >= 0 && out_kind <= 2 && (out_kind == 2 ? res != nullptr : out != nullptr),
+               "gate / out kind");
+    dim3 grid(rows, groups);
+    const uint16_t *gb = (const uint16_t*)gate_bias_bf16, *w = (const uint16_t*)w_bf16;
+#define KF_GN(G, A, T) kf_group_norm_kernel<G, A, T><<<grid, 256, 0, ctx->stream>>>((T*)out, ldo, res, x, ldx, gate, ldg, gb, w, row_idx, dim, groups, eps, mult)
+    if (out_kind == 2) {
+        if (gate_kind == 0) KF_GN(0, true, float);
+        else if (gate_kind == 1) KF_GN(1, true, float);
+        else KF_GN(2, true, float);
+    } else if (out_kind == 1) {
+        if (gate_kind == 0) KF_GN(0, false, float);
+        else if (gate_kind == 1) KF_GN(1, false, float);
+        else KF_GN(2, false, float);
+    } else {
+        if (gate_kind == 0) KF_GN(0, false, uint16_t);
+        else if (gate_kind == 1) KF_GN(1, false, uint16_t);
+        else KF_GN(2, false, uint16_t);
+    }
+#undef KF_GN
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+extern "C" int kf_f32_to_bf16(kf_ctx* ctx, void* out_bf16, const float* in, size_t n) {
+    if (!ctx || !out_bf16 || !in) return KF_ERR_BAD_ARG;
+    if (!n) return KF_OK;
+    kf_f32_to_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>((uint16_t*)out_bf16, in, n);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+
+// Router of a mixture of experts over fp32 logits [M][ldl] (+ bf16 bias [E] or NULL): idx / wgt [M][top]; then the dispatch tables:
+// offsets [E + 1], entry_slot [M * top] (where each (token, choice) sits among the expert-sorted slots), slot_row / slot_group [M * top].
+// work: device int32 scratch of 2 * M * top + E entries.
+extern "C" int kf_moe_route(kf_ctx* ctx, int32_t* idx, float* wgt, int32_t* offsets, int32_t* entry_slot, int32_t* slot_row, int32_t* slot_group,
+                            int32_t* work, const float* logits, int ldl, const void* bias_bf16, int M, int E, int top) {
+    if (!ctx || !idx || !wgt || !offsets || !entry_slot || !slot_row || !slot_group || !work || !logits) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, M >= 1 && E >= 1 && top >= 1 && top <= E && ldl >= E, "1 <= top <= experts");
+    const int n = M * top;
+    int32_t *rank = work, *count = work + n;
+    kf_moe_route_kernel<<<(M + 3) / 4, 128, 0, ctx->stream>>>(idx, wgt, logits, ldl, (const uint16_t*)bias_bf16, M, E, top);
+    KF_LAUNCH_CHECK(ctx);
+    kf_moe_rank_kernel<<<E, 256, 0, ctx->stream>>>(rank, count, idx, n);
+    KF_LAUNCH_CHECK(ctx);
+    kf_moe_offsets_kernel<<<1, 32, 0, ctx->stream>>>(offsets, count, E);
+    KF_LAUNCH_CHECK(ctx);
+    kf_moe_slots_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>(entry_slot, slot_row, slot_group, idx, rank, offsets, n, top);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+extern "C" int kf_moe_combine(kf_ctx* ctx, float* out, const float* y_slots, const int32_t* entry_slot, const float* wgt, const float* shared,
+                              const float* shared_gate_logit, int M, int dim, int top) {
+    if (!ctx || !out || !y_slots || !entry_slot || !wgt) return KF_ERR_BAD_ARG;
+    kf_moe_combine_kernel<<<M, 256, 0, ctx->stream>>>(out, y_slots, entry_slot, wgt, shared, shared_gate_logit, dim, top);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}

@@ -1,0 +1,362 @@
+// seqmix.cu -- sequence mixers beside the GQA attention of attention.cu:
+//   (1) selective state-space mixing (state-space duality form): a short causal convolution per channel with SiLU, then per head the
+//       recurrence  S_t = exp(-exp(A) dt_t) S_{t-1} + dt_t B_t x_t^T,  y_t = S_t^T C_t + D x_t  with S an [N x P] fp32 state per
+//       (sequence slot, head) that persists between calls, like the K/V rows of the attention cache;
+//   (2) attention over a compressed latent: every cached row holds the normalised latent c (rank r) and ONE rotated key part shared by
+//       all heads; queries are absorbed into latent space (q' = W_uk^T q), scores and the softmax -- whose denominator also holds a
+//       learned per-head sink term -- run in fp32 over the cached rows, and the attended latent is expanded per head by W_uv.
+// Everything that enters the recurrence or the softmax is fp32; the cache rows are stored in the activation type (bf16 bits, or float
+// for a model run entirely in 32-bit).  A token m carries (pos[m], slot[m]); a slot whose first token has position 0 starts from a
+// zero state without any clearing pass.  Tokens are laid out as nseq sequences of T consecutive tokens each (prefill panel: 1 x M;
+// batched decode: M x 1).  No reference equivalent (the reference has neither mixer on its inference path).
+#include <math.h>
+
+#include <algorithm>
+
+#include "kf_common.cuh"
+
+namespace {
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// ------------------------------------------------------------------------------------------------------------ causal convolution
+// out[m][c] = silu(b[c] + sum_j w[c][j] * in(t - (K-1-j))), in(t') = u[t'] inside the panel, the slot's stored tail before it, 0 before
+// the start of the sequence.  tail: [slot][K-1][C], oldest first.
+__global__ void kf_conv_silu_kernel(float* __restrict__ out, const float* __restrict__ u, int ldu, const uint16_t* __restrict__ w, const uint16_t* __restrict__ b,
+                                    const float* __restrict__ tail, size_t tail_stride, const int32_t* __restrict__ pos, const int32_t* __restrict__ slot,
+                                    int T, int C, int K) {
+    const int m = blockIdx.x, seq = m / T, t = m - seq * T;
+    const int p = pos[m];
+    const float* tl = tail + (size_t)slot[m] * tail_stride;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float s = b ? bf16_bits_to_f32(b[c]) : 0.f;
+        for (int j = 0; j < K; j++) {
+            const int back = K - 1 - j;
+            if (p - back < 0) continue;  // before the sequence started
+            float v;
+            if (t - back >= 0) v = u[(size_t)(m - back) * ldu + c];
+            else v = tl[(size_t)(K - 1 + (t - back)) * C + c];  // t - back in [-(K-1), -1]
+            s = fmaf(bf16_bits_to_f32(w[(size_t)c * K + j]), v, s);
+        }
+        out[(size_t)m * C + c] = s * sigmoid_f(s);
+    }
+}
+// the new tail of each sequence: its last K-1 inputs (a thread owns a channel and walks oldest -> newest, so the in-place shift is safe)
+__global__ void kf_conv_tail_kernel(float* __restrict__ tail, size_t tail_stride, const float* __restrict__ u, int ldu, const int32_t* __restrict__ pos,
+                                    const int32_t* __restrict__ slot, int T, int C, int K) {
+    const int seq = blockIdx.x, m0 = seq * T;
+    float* tl = tail + (size_t)slot[m0] * tail_stride;
+    const int p0 = pos[m0];
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        for (int i = 0; i < K - 1; i++) {
+            const int t = T - (K - 1) + i;  // panel-relative index of the input that lands in tail[i]
+            float v;
+            if (t >= 0) v = u[(size_t)(m0 + t) * ldu + c];
+            else v = (p0 + t >= 0) ? tl[(size_t)(K - 1 + t) * C + c] : 0.f;
+            tl[(size_t)i * C + c] = v;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------ selective scan
+// grid (heads, sequences, p-chunks).  Thread (p, r) keeps NPT consecutive state rows n of column p in registers; the R threads of a
+// column are adjacent lanes and reduce y with shuffles.  Tokens are staged through shared memory TB at a time.
+constexpr int NPT = 16, TB = 16;
+__global__ void __launch_bounds__(1024) kf_ssm_scan_kernel(float* __restrict__ y, int ldy, const float* __restrict__ xbc, int C, const float* __restrict__ u,
+                                                           int ldu, int z_unused, int dt_off, const uint16_t* __restrict__ dt_bias,
+                                                           const uint16_t* __restrict__ A_log, const uint16_t* __restrict__ Dw, float* __restrict__ state,
+                                                           size_t state_stride, const int32_t* __restrict__ pos, const int32_t* __restrict__ slot, int T,
+                                                           int H, int P, int N, int G, int R, int PB) {
+    extern __shared__ float sm[];
+    float* sB  = sm;                 // [TB][N]
+    float* sC  = sB + TB * N;        // [TB][N]
+    float* sX  = sC + TB * N;        // [TB][PB]
+    float* sDt = sX + TB * PB;       // [TB]
+    float* sA  = sDt + TB;           // [TB]
+    const int h = blockIdx.x, seq = blockIdx.y, p0 = blockIdx.z * PB;
+    const int g = h / (H / G), inner = H * P;
+    const int tid = threadIdx.x, pl = tid / R, r = tid - pl * R, p = p0 + pl;
+    const bool live = pl < PB && p < P;
+    const int m0 = seq * T;
+    float* st = state + (size_t)slot[m0] * state_stride + ((size_t)h * P + (live ? p : 0)) * N;
+    float S[NPT];
+    const bool fresh = pos[m0] == 0;
+#pragma unroll
+    for (int i = 0; i < NPT; i++) {
+        const int n = r * NPT + i;
+        S[i] = (live && n < N && !fresh) ? st[n] : 0.f;
+    }
+    const float Aneg = -expf(bf16_bits_to_f32(A_log[h])), Dh = bf16_bits_to_f32(Dw[h]), dtb = bf16_bits_to_f32(dt_bias[h]);
+    for (int t0 = 0; t0 < T; t0 += TB) {
+        const int nt = min(TB, T - t0);
+        __syncthreads();
+        for (int i = tid; i < nt * N; i += blockDim.x) {
+            const int tt = i / N, n = i - tt * N;
+            const float* row = xbc + (size_t)(m0 + t0 + tt) * C;
+            sB[tt * N + n] = row[inner + g * N + n];
+            sC[tt * N + n] = row[inner + G * N + g * N + n];
+        }
+        for (int i = tid; i < nt * PB; i += blockDim.x) {
+            const int tt = i / PB, q = i - tt * PB;
+            sX[tt * PB + q] = (p0 + q < P) ? xbc[(size_t)(m0 + t0 + tt) * C + h * P + p0 + q] : 0.f;
+        }
+        if (tid < nt) {
+            const float dtv = softplus_f(u[(size_t)(m0 + t0 + tid) * ldu + dt_off + h] + dtb);
+            sDt[tid] = dtv, sA[tid] = expf(Aneg * dtv);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; tt++) {
+            const float dtv = sDt[tt], av = sA[tt], xv = sX[tt * PB + (pl < PB ? pl : 0)];
+            const float dx = dtv * xv;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < NPT; i++) {
+                const int n = r * NPT + i;
+                if (n < N) {
+                    S[i] = fmaf(av, S[i], dx * sB[tt * N + n]);
+                    acc  = fmaf(S[i], sC[tt * N + n], acc);
+                }
+            }
+            for (int o = R >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (live && r == 0) y[(size_t)(m0 + t0 + tt) * ldy + h * P + p] = fmaf(Dh, xv, acc);
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < NPT; i++) {
+            const int n = r * NPT + i;
+            if (n < N) st[n] = S[i];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------ latent attention
+// cache row = [c (rank) | rotated shared key (rot_dim)].  One block per token: RMS norm of the first `rank` entries of the down
+// projection times w; rotate-half on the first `dims` entries of the rest (pair i <-> i + dims/2, angle pos * inv_freq[i], fp32 angle,
+// sine / cosine evaluated in double).
+template <typename TC>
+__global__ void __launch_bounds__(256) kf_latent_append_kernel(TC* __restrict__ cache, size_t slot_stride, const float* __restrict__ ckr, int ldc,
+                                                               const uint16_t* __restrict__ w, const float* __restrict__ inv_freq,
+                                                               const int32_t* __restrict__ pos, const int32_t* __restrict__ slot, int rank, int rot_dim,
+                                                               int dims, float eps) {
+    __shared__ float red[32];
+    const int m = blockIdx.x, W = rank + rot_dim;
+    const float* in = ckr + (size_t)m * ldc;
+    TC* row = cache + (size_t)slot[m] * slot_stride + (size_t)pos[m] * W;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) ss = fmaf(in[i], in[i], ss);
+    ss = block_sum(ss, red);
+    const float s = 1.0f / sqrtf(ss / (float)rank + eps);
+    auto put = [&](int i, float v) {
+        if (sizeof(TC) == 2) ((uint16_t*)row)[i] = f32_to_bf16_bits(v);
+        else ((float*)row)[i] = v;
+    };
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) put(i, in[i] * s * bf16_bits_to_f32(w[i]));
+    const int half = dims / 2;
+    const float fp = (float)pos[m];
+    for (int i = threadIdx.x; i < rot_dim; i += blockDim.x) {
+        float v = in[rank + i];
+        if (i < dims) {
+            const int j = i < half ? i : i - half;
+            const float ang = fp * inv_freq[j];
+            double sn, cs;
+            sincos((double)ang, &sn, &cs);
+            const float a = in[rank + j], b = in[rank + j + half];
+            v = i < half ? a * (float)cs - b * (float)sn : b * (float)cs + a * (float)sn;
+        }
+        put(rank + i, v);
+    }
+}
+// q' [M][H][rank + rot_dim] = scale * [ W_uk[h]^T q_plain[h]  |  rotate(q_rot[h]) ]; one block per (token, head)
+__global__ void __launch_bounds__(128) kf_latent_query_kernel(float* __restrict__ qa, const float* __restrict__ q, int ldq, const uint16_t* __restrict__ Wuk,
+                                                              const float* __restrict__ inv_freq, const int32_t* __restrict__ pos, int H, int dn, int rot_dim,
+                                                              int dims, int rank, float scale) {
+    extern __shared__ float sq[];  // [dn + rot_dim]
+    const int m = blockIdx.x, h = blockIdx.y, D = dn + rot_dim;
+    const float* qh = q + (size_t)m * ldq + (size_t)h * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) sq[i] = qh[i];
+    __syncthreads();
+    float* o = qa + ((size_t)m * H + h) * (rank + rot_dim);
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        float s = 0.f;
+        for (int d = 0; d < dn; d++) s = fmaf(sq[d], bf16_bits_to_f32(Wuk[((size_t)h * dn + d) * rank + c]), s);
+        o[c] = s * scale;
+    }
+    const int half = dims / 2;
+    const float fp = (float)pos[m];
+    for (int i = threadIdx.x; i < rot_dim; i += blockDim.x) {
+        float v = sq[dn + i];
+        if (i < dims) {
+            const int j = i < half ? i : i - half;
+            const float ang = fp * inv_freq[j];
+            double sn, cs;
+            sincos((double)ang, &sn, &cs);
+            const float a = sq[dn + j], b = sq[dn + j + half];
+            v = i < half ? a * (float)cs - b * (float)sn : b * (float)cs + a * (float)sn;
+        }
+        o[rank + i] = v * scale;
+    }
+}
+// One block (4 warps) per (token, head): warp w takes keys w, w + 4, ...; a lane owns elements lane, lane + 32, ... of a row.  Online
+// softmax per warp, merged in shared memory; the sink joins the denominator once: den += exp(sink - max).  out = sum_j p_j c_j / den.
+constexpr int LMAX = 16;  // elements per lane: rank + rot_dim <= 512
+template <typename TC>
+__global__ void __launch_bounds__(128) kf_latent_attn_kernel(float* __restrict__ out, const float* __restrict__ qa, const TC* __restrict__ cache,
+                                                             size_t slot_stride, const uint16_t* __restrict__ sink, const int32_t* __restrict__ pos,
+                                                             const int32_t* __restrict__ slot, int H, int rank, int rot_dim) {
+    extern __shared__ float sm[];  // [4][rank] accumulators + [4] max + [4] sum
+    const int m = blockIdx.x, h = blockIdx.y, W = rank + rot_dim;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* q = qa + ((size_t)m * H + h) * W;
+    float qr[LMAX], acc[LMAX];
+#pragma unroll
+    for (int i = 0; i < LMAX; i++) {
+        const int e = lane + 32 * i;
+        qr[i] = e < W ? q[e] : 0.f, acc[i] = 0.f;
+    }
+    const TC* base = cache + (size_t)slot[m] * slot_stride;
+    const int last = pos[m];
+    float mx = -INFINITY, sum = 0.f;
+    for (int j = warp; j <= last; j += 4) {
+        const TC* row = base + (size_t)j * W;
+        float kv[LMAX], s = 0.f;
+#pragma unroll
+        for (int i = 0; i < LMAX; i++) {
+            const int e = lane + 32 * i;
+            float v = 0.f;
+            if (e < W) v = sizeof(TC) == 2 ? bf16_bits_to_f32(((const uint16_t*)row)[e]) : ((const float*)row)[e];
+            kv[i] = v;
+            s     = fmaf(qr[i], v, s);
+        }
+        s = warp_sum(s);
+        const float nm = fmaxf(mx, s), corr = expf(mx - nm), pj = expf(s - nm);
+        sum = sum * corr + pj;
+#pragma unroll
+        for (int i = 0; i < LMAX; i++) acc[i] = acc[i] * corr + pj * kv[i];
+        mx = nm;
+    }
+    float* sacc = sm;
+    float* smx  = sm + 4 * rank;
+    float* ssum = smx + 4;
+#pragma unroll
+    for (int i = 0; i < LMAX; i++) {
+        const int e = lane + 32 * i;
+        if (e < rank) sacc[warp * rank + e] = acc[i];
+    }
+    if (lane == 0) smx[warp] = mx, ssum[warp] = sum;
+    __syncthreads();
+    const float sk = bf16_bits_to_f32(sink[h]);
+    float M4 = sk;
+    for (int w = 0; w < 4; w++) M4 = fmaxf(M4, smx[w]);
+    float den = expf(sk - M4), f[4];
+    for (int w = 0; w < 4; w++) f[w] = smx[w] == -INFINITY ? 0.f : expf(smx[w] - M4), den += ssum[w] * f[w];
+    float* o = out + ((size_t)m * H + h) * rank;
+    for (int e = threadIdx.x; e < rank; e += blockDim.x) {
+        float v = 0.f;
+        for (int w = 0; w < 4; w++) v += sacc[w * rank + e] * f[w];
+        o[e] = v / den;
+    }
+}
+// head outputs: o[m][h*dv + e] = (W_uv[h*dv + e] . lat[m][h]) * sigmoid(gate[m][h*dv + e]) in the activation type; warp per output
+template <typename TO>
+__global__ void __launch_bounds__(256) kf_latent_expand_kernel(TO* __restrict__ o, const float* __restrict__ lat, const uint16_t* __restrict__ Wuv,
+                                                               const float* __restrict__ gate, int ldg, int H, int dv, int rank) {
+    const int m = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* l = lat + ((size_t)m * H + h) * rank;
+    for (int e = warp; e < dv; e += 8) {
+        const uint16_t* w = Wuv + ((size_t)h * dv + e) * rank;
+        float s = 0.f;
+        for (int c = lane; c < rank; c += 32) s = fmaf(l[c], bf16_bits_to_f32(w[c]), s);
+        s = warp_sum(s);
+        if (lane == 0) {
+            const size_t idx = (size_t)m * H * dv + (size_t)h * dv + e;
+            const float v    = gate ? s * sigmoid_f(gate[(size_t)m * ldg + h * dv + e]) : s;
+            if (sizeof(TO) == 2) ((uint16_t*)o)[idx] = f32_to_bf16_bits(v);
+            else ((float*)o)[idx] = v;
+        }
+    }
+}
+}  // namespace
+
+// xbc_out [M][C] = silu(conv(u[:, c0 : c0 + C])) per channel; then the slot's tail is advanced.  u: float [M][ldu]; w bf16 [C][K]; b bf16 [C].
+extern "C" int kf_conv_silu(kf_ctx* ctx, float* xbc_out, const float* u, int ldu, int c0, const void* w_bf16, const void* b_bf16, float* tail,
+                            size_t tail_stride, const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int C, int K) {
+    if (!ctx || !xbc_out || !u || !w_bf16 || !tail || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, nseq >= 1 && T >= 1 && C >= 1 && K >= 1 && tail_stride >= (size_t)(K - 1) * C, "shape");
+    kf_conv_silu_kernel<<<nseq * T, 256, 0, ctx->stream>>>(xbc_out, u + c0, ldu, (const uint16_t*)w_bf16, (const uint16_t*)b_bf16, tail, tail_stride, pos_dev,
+                                                           slot_dev, T, C, K);
+    KF_LAUNCH_CHECK(ctx);
+    if (K > 1) {
+        kf_conv_tail_kernel<<<nseq, 256, 0, ctx->stream>>>(tail, tail_stride, u + c0, ldu, pos_dev, slot_dev, T, C, K);
+        KF_LAUNCH_CHECK(ctx);
+    }
+    return KF_OK;
+}
+// y [M][ldy] (heads x P) from xbc [M][C = H*P + 2*G*N] (x | B | C after the convolution) and the step logits u[:, dt_off + h];
+// state: float [slot][H][P][N] with state_stride floats per slot.
+extern "C" int kf_ssm_scan(kf_ctx* ctx, float* y, int ldy, const float* xbc, const float* u, int ldu, int dt_off, const void* dt_bias_bf16,
+                           const void* A_log_bf16, const void* D_bf16, float* state, size_t state_stride, const int32_t* pos_dev, const int32_t* slot_dev,
+                           int nseq, int T, int H, int P, int N, int G) {
+    if (!ctx || !y || !xbc || !u || !dt_bias_bf16 || !A_log_bf16 || !D_bf16 || !state || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, nseq >= 1 && T >= 1 && H >= 1 && P >= 1 && N >= 1 && G >= 1 && H % G == 0 && N <= 32 * NPT, "state size <= 512, groups divide heads");
+    KF_REQUIRE(ctx, state_stride >= (size_t)H * P * N, "state stride");
+    int R = 1;
+    while (R * NPT < N) R <<= 1;
+    const int PB = std::min(P, 1024 / R);
+    const int threads = ((PB * R + 31) / 32) * 32;
+    const size_t smem = (size_t)(2 * TB * N + TB * PB + 2 * TB) * sizeof(float);
+    KF_REQUIRE(ctx, smem <= 48 * 1024, "state too large for the staging area");
+    dim3 grid(H, nseq, (P + PB - 1) / PB);
+    kf_ssm_scan_kernel<<<grid, threads, smem, ctx->stream>>>(y, ldy, xbc, H * P + 2 * G * N, u, ldu, 0, dt_off, (const uint16_t*)dt_bias_bf16,
+                                                            (const uint16_t*)A_log_bf16, (const uint16_t*)D_bf16, state, state_stride, pos_dev, slot_dev, T,
+                                                            H, P, N, G, R, PB);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+
+extern "C" int kf_latent_append(kf_ctx* ctx, void* cache, int cache_f32, size_t slot_stride, const float* ckr, int ldc, const void* norm_w_bf16,
+                                const float* inv_freq_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int rank, int rot_dim, int rot_dims,
+                                float eps) {
+    if (!ctx || !cache || !ckr || !norm_w_bf16 || !inv_freq_dev || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, M >= 1 && rank >= 1 && rot_dim >= 0 && rot_dims >= 0 && rot_dims <= rot_dim && rot_dims % 2 == 0, "rotated dims: even, <= rot_dim");
+    if (cache_f32)
+        kf_latent_append_kernel<float><<<M, 256, 0, ctx->stream>>>((float*)cache, slot_stride, ckr, ldc, (const uint16_t*)norm_w_bf16, inv_freq_dev, pos_dev,
+                                                                  slot_dev, rank, rot_dim, rot_dims, eps);
+    else
+        kf_latent_append_kernel<uint16_t><<<M, 256, 0, ctx->stream>>>((uint16_t*)cache, slot_stride, ckr, ldc, (const uint16_t*)norm_w_bf16, inv_freq_dev,
+                                                                     pos_dev, slot_dev, rank, rot_dim, rot_dims, eps);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+// lat_out [M][H][rank]: attention of every (token, head) over the rows 0 .. pos[m] of its slot.  q: float [M][ldq], heads laid out as
+// [dn plain | rot_dim rotated]; w_uk bf16 [H*dn][rank]; sink bf16 [H]; qa_work: float scratch [M][H][rank + rot_dim].
+extern "C" int kf_latent_attention(kf_ctx* ctx, float* lat_out, float* qa_work, const float* q, int ldq, const void* w_uk_bf16, const void* sink_bf16,
+                                   const void* cache, int cache_f32, size_t slot_stride, const float* inv_freq_dev, const int32_t* pos_dev,
+                                   const int32_t* slot_dev, int M, int H, int dn, int rot_dim, int rot_dims, int rank, float scale) {
+    if (!ctx || !lat_out || !qa_work || !q || !w_uk_bf16 || !sink_bf16 || !cache || !inv_freq_dev || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, M >= 1 && H >= 1 && dn >= 1 && rank >= 1 && rank + rot_dim <= 32 * LMAX && rot_dims <= rot_dim && rot_dims % 2 == 0, "rank + rot_dim <= 512");
+    dim3 grid(M, H);
+    kf_latent_query_kernel<<<grid, 128, (size_t)(dn + rot_dim) * 4, ctx->stream>>>(qa_work, q, ldq, (const uint16_t*)w_uk_bf16, inv_freq_dev, pos_dev, H, dn,
+                                                                                 rot_dim, rot_dims, rank, scale);
+    KF_LAUNCH_CHECK(ctx);
+    const size_t smem = (size_t)(4 * rank + 8) * 4;
+    if (cache_f32)
+        kf_latent_attn_kernel<float><<<grid, 128, smem, ctx->stream>>>(lat_out, qa_work, (const float*)cache, slot_stride, (const uint16_t*)sink_bf16, pos_dev,
+                                                                      slot_dev, H, rank, rot_dim);
+    else
+        kf_latent_attn_kernel<uint16_t><<<grid, 128, smem, ctx->stream>>>(lat_out, qa_work, (const uint16_t*)cache, slot_stride, (const uint16_t*)sink_bf16,
+                                                                         pos_dev, slot_dev, H, rank, rot_dim);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+extern "C" int kf_latent_expand(kf_ctx* ctx, void* out, int out_f32, const float* lat, const void* w_uv_bf16, const float* gate_logit, int ldg, int M, int H,
+                                int dv, int rank) {
+    if (!ctx || !out || !lat || !w_uv_bf16) return KF_ERR_BAD_ARG;
+    dim3 grid(M, H);
+    if (out_f32)
+        kf_latent_expand_kernel<float><<<grid, 256, 0, ctx->stream>>>((float*)out, lat, (const uint16_t*)w_uv_bf16, gate_logit, ldg, H, dv, rank);
+    else
+        kf_latent_expand_kernel<uint16_t><<<grid, 256, 0, ctx->stream>>>((uint16_t*)out, lat, (const uint16_t*)w_uv_bf16, gate_logit, ldg, H, dv, rank);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}

@@ -27,8 +27,17 @@ static int jint(const JSON& j, std::initializer_list<const char*> path, int dflt
 MODEL_CARD MODEL_CARD::FromJSON(const JSON& j0) {
     MODEL_CARD c;
     const JSON* hf = j0.find("hf_config");
-    if (!hf && j0.contains("hidden_size")) hf = &j0;
-    if (hf) {  // HF config.json (MODEL_CARD::InitHugFace, src/Utils/CLI_params.cpp:2224-2300)
+    if (!hf && (j0.contains("hidden_size") || j0.contains("architecture"))) hf = &j0;
+    const ARCH_ENTRY* entry = nullptr;
+    if (hf)
+        if (const JSON* a = hf->find("architecture")) {  // a checkpoint's config.json that names its architecture: the registry parses it
+            c.arch = a->as_string(c.arch);
+            entry  = FindArch(c.arch);
+            if (!entry) throw std::runtime_error("architecture '" + c.arch + "' is not registered");
+        }
+    if (entry && entry->parse) {
+        entry->parse(*hf, c);
+    } else if (hf) {  // HF config.json (MODEL_CARD::InitHugFace, src/Utils/CLI_params.cpp:2224-2300)
         const JSON& h = *hf;
         c.n_embd    = jint(h, {"hidden_size"}, 0);
         c.n_ff      = jint(h, {"intermediate_size"}, 0);
@@ -78,13 +87,47 @@ MODEL_CARD MODEL_CARD::FromJSON(const JSON& j0) {
     if (const JSON* s = j0.path({"init", "norm_sigma"})) c.norm_sigma = (float)s->as_double(c.norm_sigma);
     std::string a = c.arch;
     std::transform(a.begin(), a.end(), a.begin(), ::toupper);
-    if (a != "QWEN3") throw std::runtime_error("model.arch '" + c.arch + "' is outside the hot path (only QWEN3 is built)");
+    if (!FindArch(a)) throw std::runtime_error("model.arch '" + c.arch + "' is outside the hot path (registered: QWEN3, SIPAZEN)");
+    if (const JSON* s = j0.path({"gpt", "compute_dtype"})) c.compute_f32 = s->as_string("") == "float32";
+    c.logit_rows_cfg = jint(j0, {"gpt", "logit_rows"}, c.logit_rows_cfg);
+    if (c.max_seq_len <= 0 || c.max_batch <= 0) throw std::runtime_error("gpt.max_seq_len / gpt.max_batch must be positive");
+    if (c.IsHybrid()) return c;  // the architecture's parser has checked its own sizes
+    if (c.compute_f32) throw std::runtime_error("gpt.compute_dtype float32: this architecture runs in bf16 only");
     if (c.n_layers <= 0 || c.n_embd <= 0 || c.n_ff <= 0 || c.n_head <= 0 || c.n_head_kv <= 0 || c.head_dim <= 0 || c.vocab <= 0)
         throw std::runtime_error("model config incomplete: need Layer/Embed/Ffn/Head/KVHead/head_dim");
     if (c.n_head % c.n_head_kv) throw std::runtime_error("Head must be a multiple of KVHead");
     if (c.head_dim != 64 && c.head_dim != 128) throw std::runtime_error("head_dim must be 64 or 128");
     if (c.max_seq_len <= 0 || c.max_batch <= 0) throw std::runtime_error("gpt.max_seq_len / gpt.max_batch must be positive");
     return c;
+}
+
+// ------------------------------------------------------------------------------------------------------------ registry
+static int BuildQwen3(Fish& f);
+static int ForwardQwen3(Fish& f, int M, bool want_logits);
+const ARCH_ENTRY* FindArch(const std::string& name) {
+    static const ARCH_ENTRY qwen3 = {"QWEN3", nullptr, BuildQwen3, ForwardQwen3, nullptr};
+    std::string a = name;
+    std::transform(a.begin(), a.end(), a.begin(), ::toupper);
+    const ARCH_ENTRY* all[] = {&qwen3, SipazenArch()};
+    for (const ARCH_ENTRY* e : all)
+        if (a == e->name) return e;
+    return nullptr;
+}
+void SeqStateCache::InitSlots(int n) {
+    max_batch = n;
+    free_slots.clear();
+    for (int i = n - 1; i >= 0; i--) free_slots.push_back(i);
+}
+int SeqStateCache::Acquire() {
+    if (free_slots.empty()) return -1;
+    const int s = free_slots.back();
+    free_slots.pop_back();
+    return s;
+}
+bool SeqStateCache::Release(int slot) {
+    if (slot < 0 || slot >= max_batch || std::find(free_slots.begin(), free_slots.end(), slot) != free_slots.end()) return false;
+    free_slots.push_back(slot);
+    return true;
 }
 
 // ------------------------------------------------------------------------------------------------------------ neurons
@@ -218,14 +261,19 @@ Fish::Fish(kf_ctx* c, const MODEL_CARD& card, int rank, int world) : ctx(c), con
 Fish::~Fish() {
     ResetGraphs();
     tensors.clear();
-    void* bufs[] = {x, xb, q, k, v, att, hb, logits, part_f32, d_tokens, d_pos, d_next, d_rng, cache.key, cache.value};
+    blocks.clear();
+    void* bufs[] = {x, xb, q, k, v, att, hb, logits, part_f32, d_tokens, d_pos, d_next, d_rng, cache.key, cache.value, d_slot, d_sel, logits_f32};
     for (void* b : bufs)
         if (b) kf_free(ctx, b);
+    for (void* b : owned)
+        if (b) kf_free(ctx, b);
+    if (h_logits_f32) kf_host_free(h_logits_f32);
     if (rope_table_shared) kf_free(ctx, rope_table_shared);
     if (h_stage) kf_host_free(h_stage);
     if (h_logits) kf_host_free(h_logits);
 }
 void Fish::ResetGraphs() {
+    tables_ready  = false;
     weights_dirty = true;  // every path that changes a resident tensor ends here: kf_model_info_get recounts the resident bytes once
     for (auto& g : graphs)
         if (g.second) kf_graph_destroy(g.second);
@@ -253,6 +301,17 @@ int Fish::AllocTensor(const std::string& name, int rows, int cols, int id, hGTen
 // Fish::MakeInstance -> QWen3 ctor -> Build (reference src/Manifold/Fish.cpp:13-95; SelfAttention::Build TGraph.cpp:94-165;
 // FFN::Build EmbedVAE.cpp:427-480; tensor names NN2NAME QWen.cpp:61-145)
 int Fish::Build() {
+    arch = FindArch(config.arch);
+    if (!arch) {
+        error = "architecture '" + config.arch + "' is not registered";
+        return KF_ERR_BAD_ARG;
+    }
+    states.InitSlots(config.max_batch);
+    return arch->build(*this);
+}
+static int BuildQwen3(Fish& f) { return f.BuildQwen3(); }
+static int ForwardQwen3(Fish& f, int M, bool want_logits) { return f.ForwardQwen3(M, want_logits); }
+int Fish::BuildQwen3() {
     std::string* hFishErr = &error;
     const MODEL_CARD& c = config;
     const int W = tp_world;
@@ -328,7 +387,9 @@ int Fish::Build() {
     KF_TRY(kf_malloc(ctx, T * 4, (void**)&d_tokens));
     KF_TRY(kf_malloc(ctx, T * 4, (void**)&d_pos));
     KF_TRY(kf_malloc(ctx, T * 4, (void**)&d_next));
-    KF_TRY(kf_host_alloc(T * 4 * 3, (void**)&h_stage));
+    KF_TRY(kf_malloc(ctx, T * 4, (void**)&d_slot));
+    KF_TRY(kf_malloc(ctx, T * 4, (void**)&d_sel));
+    KF_TRY(kf_host_alloc(T * 4 * 5, (void**)&h_stage));
     KF_TRY(kf_host_alloc((size_t)logit_rows * c.vocab * 2, (void**)&h_logits));
     // one rope table shared by all layers
     void* table = nullptr;
@@ -597,7 +658,8 @@ hGTensor Fish::GetTensor(const std::string& name) const {
 }
 
 // Fish::ForwardOnRLS (reference src/Manifold/gLLM.cpp:755-769): run every neuron's cuInfer in graph order
-int Fish::ForwardOnRLS(int M, bool want_logits) {
+int Fish::ForwardOnRLS(int M, bool want_logits) { return arch->forward(*this, M, want_logits); }
+int Fish::ForwardQwen3(int M, bool want_logits) {
     std::string* hFishErr = &error;
     // tensor-parallel decode of up to 8 tokens: the exchange after O / down is the epilogue of those matmuls (kf_tp.cuh): 5 launches
     // per block instead of 7
@@ -650,13 +712,26 @@ int Fish::CtxBucket() const {
     while ((1 << b) < staged_pos_max + 1 && (1 << b) < config.max_seq_len) b++;
     return b;
 }
-int Fish::UseGraph(int M, bool want_logits) {
+uint64_t Fish::UseGraph(int M, bool want_logits) {
     attn_hint = std::min(config.max_seq_len, 1 << CtxBucket()) - 1;
-    return (M << 12) | (CtxBucket() << 7) | (int)want_logits | (seq_mode << 1) | ((int)last_only << 5) | ((int)panel_consecutive << 6);
+    return ((uint64_t)n_rows << 40) | ((uint64_t)M << 12) | (CtxBucket() << 7) | (int)want_logits | (seq_mode << 1) | ((int)last_only << 5) | ((int)panel_consecutive << 6);
 }
 
 int Fish::Forward(const int32_t* tokens, const int32_t* pos, int M, int mode, uint16_t* logits_out, int32_t* next_out) {
+    return ForwardEx(tokens, pos, M, mode, 0, nullptr, 0, logits_out, nullptr, next_out);
+}
+int Fish::ForwardEx(const int32_t* tokens, const int32_t* pos, int M, int mode, int slot, const int32_t* sel, int n_sel, uint16_t* logits_out,
+                    float* logits_f32_out, int32_t* next_out) {
     std::string* hFishErr = &error;
+    const bool hybrid = config.IsHybrid();
+    if (!hybrid && (slot != 0 || sel || logits_f32_out)) {
+        error = "Forward: sequence slots, row selection and fp32 logits belong to the hybrid stacks";
+        return KF_ERR_BAD_ARG;
+    }
+    if (slot < 0 || slot >= config.max_batch || (sel && (n_sel < 1 || n_sel > M)) || (mode == 1 && slot != 0)) {
+        error = "Forward: slot must be below gpt.max_batch (and 0 in mode 1); 1 <= n_sel <= M";
+        return KF_ERR_BAD_ARG;
+    }
     KF_TRY(kf_ctx_make_current(ctx));
     if (!tokens || !pos || M < 1 || M > max_tokens) {
         error = "Forward: 1 <= M <= " + std::to_string(max_tokens);
@@ -672,6 +747,7 @@ int Fish::Forward(const int32_t* tokens, const int32_t* pos, int M, int mode, ui
             return KF_ERR_BAD_ARG;
         }
         h_stage[m] = tokens[m], h_stage[max_tokens + m] = pos[m];
+        h_stage[3 * max_tokens + m] = mode == 1 ? m : slot;
     }
     if (!all_resident) {  // a model whose weights come tensor by tensor (SetTensor / SetTensorAWQ / a checkpoint) must have all of them
         for (auto& kv : tensors)
@@ -688,15 +764,30 @@ int Fish::Forward(const int32_t* tokens, const int32_t* pos, int M, int mode, ui
     last_only = mode == 2;
     panel_consecutive = seq_mode == 0;
     for (int m = 1; m < M && panel_consecutive; m++) panel_consecutive = pos[m] == pos[0] + m;
-    const int R = last_only ? 1 : M;  // rows of logits / argmax produced
-    if ((logits_out || next_out) && R > logit_rows) {
+    const int R = sel ? n_sel : last_only ? 1 : M;  // rows of logits / argmax produced
+    for (int r = 0; r < R && R <= max_tokens; r++) {
+        const int src = sel ? sel[r] : last_only ? M - 1 : r;
+        if (src < 0 || src >= M) {
+            error = "Forward: a selected row is outside the step's tokens";
+            return KF_ERR_BAD_ARG;
+        }
+        h_stage[4 * max_tokens + r] = src;
+    }
+    n_rows = hybrid ? R : 0;
+    if ((logits_out || next_out || logits_f32_out) && R > logit_rows) {
         error = "Forward: logits of more than " + std::to_string(logit_rows) + " tokens requested; use seq_mode 2 (last token only) for long panels";
         return KF_ERR_BAD_ARG;
     }
     KF_TRY(kf_h2d(ctx, d_tokens, h_stage, (size_t)M * 4));
     KF_TRY(kf_h2d(ctx, d_pos, h_stage + max_tokens, (size_t)M * 4));
-    const bool want_logits = logits_out || next_out;
-    const int key          = UseGraph(M, want_logits) | ((next_out ? 1 : 0) << 3);
+    if (hybrid) {
+        KF_TRY(kf_h2d(ctx, d_slot, h_stage + 3 * max_tokens, (size_t)M * 4));
+        KF_TRY(kf_h2d(ctx, d_sel, h_stage + 4 * max_tokens, (size_t)R * 4));
+        if (!tables_ready && arch->prepare) KF_TRY(arch->prepare(*this));
+        tables_ready = true;
+    }
+    const bool want_logits = logits_out || next_out || logits_f32_out;
+    const uint64_t key     = UseGraph(M, want_logits) | ((next_out ? 1 : 0) << 3);
     auto it                = graphs.find(key);
     if (use_graphs && it == graphs.end() && warm.count(key)) {  // second call with this signature: capture it
         KF_TRY(kf_graph_begin(ctx));
@@ -719,11 +810,13 @@ int Fish::Forward(const int32_t* tokens, const int32_t* pos, int M, int mode, ui
         warm.insert(key);
     }
     if (logits_out) KF_TRY(kf_d2h(ctx, h_logits, logits, (size_t)R * config.vocab * 2));
+    if (logits_f32_out) KF_TRY(kf_d2h(ctx, h_logits_f32, logits_f32, (size_t)R * config.vocab * 4));
     if (next_out) KF_TRY(kf_d2h(ctx, h_stage + 2 * max_tokens, d_next, (size_t)R * 4));
     KF_TRY(kf_ctx_sync(ctx));
     if (logits_out) memcpy(logits_out, h_logits, (size_t)R * config.vocab * 2);
+    if (logits_f32_out) memcpy(logits_f32_out, h_logits_f32, (size_t)R * config.vocab * 4);
     if (next_out) memcpy(next_out, h_stage + 2 * max_tokens, (size_t)R * 4);
-    if (last_only && next_out) {  // leave the model ready for DecodeLoop(n, 1): feed the sampled token at the next position
+    if (last_only && next_out && !sel) {  // leave the model ready for DecodeLoop(n, 1): feed the sampled token at the next position
         h_stage[0] = next_out[0], h_stage[max_tokens] = pos[M - 1] + 1;
         KF_TRY(kf_h2d(ctx, d_tokens, h_stage, 4));
         KF_TRY(kf_h2d(ctx, d_pos, h_stage + max_tokens, 4));
@@ -811,7 +904,13 @@ int Fish::DecodeLoop(int n_steps, int M) {
     SyncGraphGeneration();
     staged_pos_max += n_steps;
     seq_mode = M > 1 ? 1 : seq_mode, last_only = false, panel_consecutive = false;
-    const int key = UseGraph(M, true) | (1 << 2);
+    n_rows = config.IsHybrid() ? M : 0;
+    if (config.IsHybrid()) {  // every decoded row is a logits row: row r comes from token r
+        for (int r = 0; r < M; r++) h_stage[4 * max_tokens + r] = r;
+        KF_TRY(kf_h2d(ctx, d_sel, h_stage + 4 * max_tokens, (size_t)M * 4));
+        KF_TRY(kf_ctx_sync(ctx));
+    }
+    const uint64_t key = UseGraph(M, true) | (1 << 2);
     auto it       = graphs.find(key);
     auto body     = [&]() -> int {
         int rc = ForwardOnRLS(M, true);

@@ -18,6 +18,27 @@
 namespace koifish {
 
 // ---- config -------------------------------------------------------------------------------------------------------------
+// One layer of a hybrid stack (config "layers": [{"type", "mixer": {...}, "mlp": {...} | null}, ...]): which sequence mixer it has, with
+// that mixer's sizes, and its feed-forward.  Layers of one model may differ in every size.
+struct MIXER_CARD {
+    std::string type;  // "mamba2" (state-space) | "latent_attention"
+    // state-space mixer: heads x vdim inner channels, state rows per head, B/C groups, gated-norm groups, convolution taps
+    int heads = 0, vdim = 0, state = 0, groups = 1, norm_groups = 1, conv = 1;
+    // latent attention: per head `dim` plain + `rot_dim` rotated query/key entries, values of vdim, latent rank; rotation on the first
+    // rot_dims entries of the rotated part with frequencies rot_base^(-2i/rot_dims); score scale
+    int dim = 0, rot_dim = 0, kv_rank = 0, rot_dims = 0;
+    float rot_base = 10000.f, scale = 1.f;
+};
+struct MOE_CARD {
+    bool present = false;
+    int experts = 0, top = 0, ff = 0;
+    int shared_ff = 0;  // 0: no shared expert
+};
+struct LAYER_CARD {
+    MIXER_CARD mixer;
+    MOE_CARD mlp;
+};
+
 struct MODEL_CARD {
     std::string arch = "QWEN3";
     int n_layers = 0, n_embd = 0, n_ff = 0, n_head = 0, n_head_kv = 0, head_dim = 128;
@@ -34,6 +55,13 @@ struct MODEL_CARD {
     int max_batch = 1;                            // independent sequences (batched decode)
     int max_prefill = 64;                         // tokens per prefill panel (gpt.max_prefill): sizes the activation buffers
     int awq_repack  = 0;                          // gpt.awq_repack: vendor AWQ tensors re-laid-out at load into PackedQ 4-bit storage (fast kernels)
+    // hybrid stacks (arch SIPAZEN): per-layer cards, grouped RMS norm, residual multiplier; fp32 residual stream
+    std::vector<LAYER_CARD> layers;
+    int norm_groups     = 1;
+    float residual_mult = 1.f;
+    bool compute_f32    = false;  // gpt.compute_dtype = "float32": activations, caches and matmuls in true 32-bit (hybrid stacks only)
+    int logit_rows_cfg  = 0;      // gpt.logit_rows: rows of the logits buffers (default max(64, max_batch))
+    bool IsHybrid() const { return !layers.empty(); }
 
     // accepts a Koifish JSON (cases/qwen3/*.json layout) or an HF config.json, optionally wrapped as {"hf_config": {...}}
     static MODEL_CARD FromJSON(const JSON& j);
@@ -42,6 +70,7 @@ struct MODEL_CARD {
 };
 
 struct Fish;
+struct HybridScratch;  // Sipazen.hpp
 bool ShardPlan(const MODEL_CARD& c, const std::string& name, int rank, int world, int* rows_g, int* cols_g, int* rows_l, int* cols_l, int* row0,
                int* col0);
 
@@ -109,6 +138,41 @@ struct KVCache {
     size_t bytes() const { return (size_t)2 * n_layer * max_batch * max_seq * kv_dim * 2; }
 };
 
+// Cache and state of a hybrid stack, per layer and per sequence slot: an attention layer keeps one row per position (latent + shared
+// rotated key, in the activation type), a state-space layer a fixed-size fp32 state (heads x vdim x state) plus the last conv - 1 inputs
+// of its convolution.  Slots are handed out and taken back by Acquire / Release; a slot is not cleared on reuse: its first token has
+// position 0 and the kernels start from zero there.
+struct SeqStateCache {
+    struct Layer {
+        void* rows = nullptr;      // [max_batch][max_seq][row_dim]
+        size_t row_stride = 0;     // elements per slot
+        int row_dim = 0;
+        float* state = nullptr;    // [max_batch][state_stride]
+        size_t state_stride = 0;
+        float* tail = nullptr;     // [max_batch][tail_stride]
+        size_t tail_stride = 0;
+    };
+    std::vector<Layer> layers;
+    int max_batch = 1, max_seq = 0;
+    bool f32 = false;
+    size_t total_bytes = 0;
+    std::vector<int> free_slots;  // LIFO: the slot released last is handed out next
+    void InitSlots(int n);
+    int Acquire();             // -1: none free
+    bool Release(int slot);    // false: not a slot in use
+};
+
+// ---- model registry: one entry per architecture name (config "architecture" / model.arch) -----------------------------------------
+struct ARCH_ENTRY {
+    const char* name;                                    // upper case
+    void (*parse)(const JSON& hf_or_root, MODEL_CARD& card);  // fills the card from the config (nullptr: the Qwen3 keys)
+    int (*build)(Fish& f);                               // tensors, neurons, caches, activation buffers
+    int (*forward)(Fish& f, int M, bool want_logits);    // one step over the staged tokens
+    int (*prepare)(Fish& f);                             // after every tensor has data (device pointer tables); may be nullptr
+};
+const ARCH_ENTRY* FindArch(const std::string& name);
+const ARCH_ENTRY* SipazenArch();  // Sipazen.cpp
+
 // ---- the model ------------------------------------------------------------------------------------------------------------
 struct Fish {
     kf_ctx* ctx = nullptr;
@@ -119,6 +183,16 @@ struct Fish {
     std::vector<std::unique_ptr<FFN>> ffn;
     Head4Token cls;
     KVCache cache;
+    const ARCH_ENTRY* arch = nullptr;
+    std::vector<std::unique_ptr<GeNeuron>> blocks;  // hybrid stacks: one block neuron per layer
+    SeqStateCache states;                           // ... and their cache / state manager
+    std::shared_ptr<HybridScratch> hscratch;        // ... and their shared activation buffers
+    std::vector<void*> owned;                       // device buffers of the architecture's own (freed with the model)
+    int32_t *d_slot = nullptr, *d_sel = nullptr;    // per token: sequence slot; per logits row: the token it is taken from
+    float* logits_f32 = nullptr;                    // hybrid stacks: fp32 logits [logit_rows][vocab]
+    float* h_logits_f32 = nullptr;                  // pinned
+    int n_rows = 0;                                 // logits rows of the current step
+    bool tables_ready = false;                      // arch->prepare ran since the last tensor change
     std::map<std::string, hGTensor> tensors;  // by HF name (NN2NAME, QWen.cpp:61-145)
     std::map<std::string, int> tensor_ids;    // synthetic-weight seed ids (shared definition with the test oracle)
 
@@ -143,8 +217,8 @@ struct Fish {
     bool tp_fuse = false;         // this forward runs the exchange as the epilogue of O / down (tensor parallel, <= 8 tokens, peer buffers)
     int attn_hint = 0;            // upper bound of the positions of the current forward (power-of-two bucket - 1): sizes the attention split
     int CtxBucket() const;        // log2 of that bucket; part of the graph key, so graphs are re-captured as the context grows
-    std::map<int, kf_graph*> graphs;  // per (M, mode) replayable token graphs
-    std::set<int> warm;               // signatures that already ran eagerly once (workspaces sized) -> next call captures
+    std::map<uint64_t, kf_graph*> graphs;  // per (M, mode) replayable token graphs
+    std::set<uint64_t> warm;               // signatures that already ran eagerly once (workspaces sized) -> next call captures
     bool use_graphs = true;
     void* rope_table_shared = nullptr;
     int staged_pos_max = 0;
@@ -157,6 +231,8 @@ struct Fish {
 
     Fish(kf_ctx* ctx, const MODEL_CARD& card, int tp_rank, int tp_world);
     ~Fish();
+    int BuildQwen3();
+    int ForwardQwen3(int M, bool want_logits);
     int Build();                 // allocate tensors + buffers (Fish::MakeInstance -> Build, Fish.cpp:13-95)
     int InitParamRandom();       // huTensor::InitParam random path + quantise at load
     int SetTensor(const std::string& hf_name, const void* host_bf16, int rows, int cols);  // SERIALIZE path: full (unsharded) tensor
@@ -168,6 +244,10 @@ struct Fish {
     int ForwardOnRLS(int M, bool want_logits);
     // public step: host tokens/pos in, logits (optional) + greedy next tokens (optional) out.  H2D/D2H inside.
     int Forward(const int32_t* tokens, const int32_t* pos, int M, int seq_mode, uint16_t* logits_out, int32_t* next_out);
+    // the same step with a sequence slot (modes 0 / 2; mode 1 uses slots 0 .. M-1), an optional choice of logits rows (sel: indices into
+    // the M tokens, n_sel <= logit_rows) and fp32 logits (hybrid stacks).  Forward() is ForwardEx(slot 0, all rows).
+    int ForwardEx(const int32_t* tokens, const int32_t* pos, int M, int seq_mode, int slot, const int32_t* sel, int n_sel, uint16_t* logits_out,
+                  float* logits_f32_out, int32_t* next_out);
     // the resident tensors exactly as they sit in HBM (data || gama per tensor): SerialGamaData, reference huTensor.cu:413-458
     int SaveBlobs(const std::string& path);
     int LoadBlobs(const std::string& path);
@@ -179,7 +259,7 @@ struct Fish {
     int Generate(const int32_t* prompt, int n_prompt, int pos0, int max_new, int eos_id, int32_t* out, int* n_out, int* stop_reason);
     // device-resident greedy loop: n_steps graph replays feeding argmax back as the next token (no host round trip)
     int DecodeLoop(int n_steps, int M);
-    int UseGraph(int M, bool want_logits);
+    uint64_t UseGraph(int M, bool want_logits);
     void ResetGraphs();
     int AllocTensor(const std::string& name, int rows, int cols, int id, hGTensor& out);
 };

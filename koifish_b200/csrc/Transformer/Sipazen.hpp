@@ -1,0 +1,71 @@
+// Sipazen.hpp -- neurons of the Sipazen hybrid stack: every layer is  x += m * norm_b(gate(h) * mixer(h)),  h = norm(x),  followed by
+// the same arrangement around a mixture-of-experts feed-forward; the mixer is either a state-space recurrence (SSMixer) or attention
+// over a compressed latent with a softmax sink (LatentAttention).  The residual stream x, the norms, the router, the recurrence and
+// the attention scores are fp32; what feeds a matmul is written in the activation type (bf16, or float when the whole model runs in
+// 32-bit).  The neurons use the model's shared scratch (HybridScratch) and its SeqStateCache; the step function, CUDA-graph replay,
+// sampler and generation loop are Fish's own.  The reference has no counterpart (its inference path is the Qwen3 block, QWen.cpp:16-145).
+#pragma once
+#include "QWen3.hpp"
+
+namespace koifish {
+
+struct HybridScratch {  // device buffers shared by all layers, sized for max_tokens
+    void* hact = nullptr;        // normed input of a sublayer, activation type [T][E]
+    float* gate_logit = nullptr; // residual-gate logits [T][E]
+    float* sub = nullptr;        // sublayer result [T][E]
+    float* u = nullptr;          // widest first projection (state-space in-projection / attention queries)
+    float* v = nullptr;          // convolution output / latent down-projection
+    float* y = nullptr;          // scan output / absorbed queries
+    float* lat = nullptr;        // attended latent [T][H][rank]
+    float* g = nullptr;          // attention output-gate logits
+    void* act = nullptr;         // input of the output projection, activation type
+    // mixture of experts
+    float* router = nullptr;     // [T][E]
+    int32_t *idx = nullptr, *offsets = nullptr, *entry_slot = nullptr, *slot_row = nullptr, *slot_group = nullptr, *work = nullptr;
+    float* wgt = nullptr;
+    void* h1 = nullptr;          // [T * top][ff] activation type
+    float* yslots = nullptr;     // [T * top][E]
+    void* hs = nullptr;          // shared expert hidden, activation type
+    float* shared = nullptr;     // [T][E]
+    float* sg = nullptr;         // [T]
+    void* head_in = nullptr;     // final norm of the selected rows, activation type
+};
+
+struct GroupNorm : GeNeuron {
+    hGTensor w;
+    int groups = 1;
+    float eps = 1e-5f;
+};
+struct SSMixer : GeNeuron {
+    MIXER_CARD card;
+    int layer = 0;
+    hGTensor in, conv, conv_b, dt_bias, A_log, D, norm, o;
+    int cuInfer(int M);  // hact -> sub
+};
+struct LatentAttention : GeNeuron {
+    MIXER_CARD card;
+    int layer = 0;
+    hGTensor q, dkv, dkv_norm, uk, uv, sink, g, o;
+    float* inv_freq = nullptr;  // device [rot_dims / 2]
+    int cuInfer(int M);
+};
+struct MoE : GeNeuron {
+    MOE_CARD card;
+    hGTensor router, router_b;
+    std::vector<hGTensor> gate, up, down;
+    hGTensor sh_gate, sh_up, sh_down, sh_sg;
+    void** tables = nullptr;  // device: [3][experts] weight pointers (gate | up | down)
+    int Prepare();
+    int cuInfer(int M);
+};
+struct HybridBlock : GeNeuron {
+    int layer = 0;
+    GroupNorm norm1, norm1b, norm2, norm2b;
+    hGTensor rg1, rg1_b, rg2, rg2_b;
+    std::unique_ptr<SSMixer> ssm;
+    std::unique_ptr<LatentAttention> attn;
+    std::unique_ptr<MoE> moe;
+    int cuInfer(int M);
+};
+
+}  // namespace koifish

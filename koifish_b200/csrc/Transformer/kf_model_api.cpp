@@ -68,7 +68,7 @@ extern "C" int kf_model_info_get(kf_model* m, kf_model_info* o) {
             if (kv.second->data) f.weight_bytes += kv.second->nByte();
         f.weights_dirty = false;
     }
-    o->weight_bytes = f.weight_bytes, o->kv_bytes = f.cache.bytes();
+    o->weight_bytes = f.weight_bytes, o->kv_bytes = f.cache.bytes() + f.states.total_bytes;
     if (!f.attn.empty()) {
         auto nb = [](const hGTensor& t) { return t ? (uint64_t)t->nByte() : 0ull; };
         SelfAttention& a = *f.attn[0];
@@ -130,6 +130,34 @@ extern "C" int kf_model_forward(kf_model* m, const int32_t* tokens, const int32_
         m->fish->error = e.what();
         return KF_ERR_BAD_ARG;
     }
+}
+extern "C" int kf_model_forward_ex(kf_model* m, const int32_t* tokens, const int32_t* pos, int M, int seq_mode, int slot, const int32_t* sel, int n_sel,
+                                   void* logits_bf16, float* logits_f32, int32_t* next) {
+    if (!m) return KF_ERR_BAD_ARG;
+    try {
+        return m->fish->ForwardEx(tokens, pos, M, seq_mode, slot, sel, n_sel, (uint16_t*)logits_bf16, logits_f32, next);
+    } catch (const std::exception& e) {
+        m->fish->error = e.what();
+        return KF_ERR_BAD_ARG;
+    }
+}
+extern "C" int kf_model_slot_acquire(kf_model* m, int* slot_out) {
+    if (!m || !slot_out) return KF_ERR_BAD_ARG;
+    const int s = m->fish->states.Acquire();
+    if (s < 0) {
+        m->fish->error = "no free sequence slot (gpt.max_batch = " + std::to_string(m->fish->config.max_batch) + ")";
+        return KF_ERR_OOM;
+    }
+    *slot_out = s;
+    return KF_OK;
+}
+extern "C" int kf_model_slot_release(kf_model* m, int slot) {
+    if (!m) return KF_ERR_BAD_ARG;
+    if (!m->fish->states.Release(slot)) {
+        m->fish->error = "slot " + std::to_string(slot) + " is not in use";
+        return KF_ERR_BAD_ARG;
+    }
+    return KF_OK;
 }
 extern "C" int kf_model_decode_loop(kf_model* m, int n_steps, int M) {
     if (!m) return KF_ERR_BAD_ARG;
