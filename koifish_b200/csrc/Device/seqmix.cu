@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(128) kf_latent_query_kernel(float* __restrict_
 }
 // One block (4 warps) per (token, head): warp w takes keys w, w + 4, ...; a lane owns elements lane, lane + 32, ... of a row.  Online
 // softmax per warp, merged in shared memory; the sink joins the denominator once: den += exp(sink - max).  out = sum_j p_j c_j / den.
-constexpr int LMAX = 16;  // elements per lane: rank + rot_dim <= 512
+constexpr int LMAX = 20;  // elements per lane: rank + rot_dim <= 640
 template <typename TC>
 __global__ void __launch_bounds__(128) kf_latent_attn_kernel(float* __restrict__ out, const float* __restrict__ qa, const TC* __restrict__ cache,
                                                              size_t slot_stride, const uint16_t* __restrict__ sink, const int32_t* __restrict__ pos,
@@ -334,7 +334,7 @@ extern "C" int kf_latent_attention(kf_ctx* ctx, float* lat_out, float* qa_work, 
                                    const void* cache, int cache_f32, size_t slot_stride, const float* inv_freq_dev, const int32_t* pos_dev,
                                    const int32_t* slot_dev, int M, int H, int dn, int rot_dim, int rot_dims, int rank, float scale) {
     if (!ctx || !lat_out || !qa_work || !q || !w_uk_bf16 || !sink_bf16 || !cache || !inv_freq_dev || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
-    KF_REQUIRE(ctx, M >= 1 && H >= 1 && dn >= 1 && rank >= 1 && rank + rot_dim <= 32 * LMAX && rot_dims <= rot_dim && rot_dims % 2 == 0, "rank + rot_dim <= 512");
+    KF_REQUIRE(ctx, M >= 1 && H >= 1 && dn >= 1 && rank >= 1 && rank + rot_dim <= 32 * LMAX && rot_dims <= rot_dim && rot_dims % 2 == 0, "rank + rot_dim <= 640");
     dim3 grid(M, H);
     kf_latent_query_kernel<<<grid, 128, (size_t)(dn + rot_dim) * 4, ctx->stream>>>(qa_work, q, ldq, (const uint16_t*)w_uk_bf16, inv_freq_dev, pos_dev, H, dn,
                                                                                  rot_dim, rot_dims, rank, scale);

@@ -1,0 +1,376 @@
+"""GPU tests of the Sipazen hybrid stack against the plain float64 restatement in sipazen_ref.py, on small random models made here.
+
+Gates: with gpt.compute_dtype = float32 the logits agree to 2e-4 (rms of the difference, mean removed, over the rms of the logits);
+in bf16 to 6e-2.  Weights are drawn on the bf16 grid, so both sides hold the same numbers.  Where random weights would hide a fault
+the weights are shaped: queries scaled up so that the softmax is peaked (one far key, a window edge or a missing sink then moves the
+logits by far more than the gate), sinks set large, decays set slow so that early tokens still matter hundreds of steps later.
+"""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import koifish_b200 as kf
+import sipazen_ref as ref
+from st_util import write_safetensors
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOL = {True: 2e-4, False: 6e-2}
+
+
+# ------------------------------------------------------------------------------------------------------------ small models
+def ssm(heads=3, vdim=8, state=24, groups=3, norm_groups=2, conv=4):
+    return {"type": "mamba2", "mixer": dict(heads=heads, vdim=vdim, state=state, groups=groups, norm_groups=norm_groups, conv=conv)}
+
+
+def att(heads=3, dim=16, rot_dim=8, rot_dims=4, vdim=12, kv_rank=40, base=500.0, scale=None):
+    return {"type": "latent_attention", "mixer": dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=kv_rank,
+                                                       rot=dict(base=base, dims=rot_dims), scale=scale or (dim + rot_dim) ** -0.5)}
+
+
+def moe(experts=5, top=2, ff=24, shared=40):
+    return {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}, "shared": ({"ff": shared} if shared else None)}
+
+
+def config(layers, width=48, vocab=96, groups=2, eps=1e-5, mult=0.6):
+    out = []
+    for mixer, mlp in layers:
+        d = dict(mixer)
+        d["mlp"] = mlp
+        out.append(d)
+    return {"architecture": "Sipazen", "vocab": vocab, "width": width, "residual_mult": mult, "norm": {"eps": eps, "groups": groups}, "layers": out}
+
+
+def bf16_grid(t):
+    return t.to(torch.bfloat16).to(torch.float32)
+
+
+def weights(cfg, seed=0, q_gain=1.0, sink=None, a_log=None):
+    g = torch.Generator().manual_seed(seed)
+    E, V = cfg["width"], cfg["vocab"]
+    W = {}
+
+    def mat(name, r, c, s=None):
+        W[name] = bf16_grid(torch.randn(r, c, generator=g) * (s if s is not None else c ** -0.5))
+
+    def vec(name, n, mean=0.0, s=0.3):
+        W[name] = bf16_grid(mean + s * torch.randn(n, generator=g))
+
+    mat("embed", V, E, 1.0)
+    mat("head", V, E)
+    vec("final.norm", E, 1.0)
+    for i, ly in enumerate(cfg["layers"]):
+        p, m = "l%d." % i, ly["mixer"]
+        for n in ("norm1", "norm1b") + (("norm2", "norm2b") if ly["mlp"] else ()):
+            vec(p + n, E, 1.0)
+        mat(p + "rg1", E, E)
+        vec(p + "rg1.b", E)
+        if ly["type"] == "mamba2":
+            inner, GN = m["heads"] * m["vdim"], m["groups"] * m["state"]
+            mat(p + "mix.in", 2 * inner + 2 * GN + m["heads"], E)
+            mat(p + "mix.conv", inner + 2 * GN, m["conv"], 0.5)
+            vec(p + "mix.conv.b", inner + 2 * GN)
+            vec(p + "mix.dt_bias", m["heads"], -1.0, 0.5)
+            vec(p + "mix.A_log", m["heads"], -1.0 if a_log is None else a_log, 0.3)
+            vec(p + "mix.D", m["heads"], 1.0)
+            vec(p + "mix.norm", inner, 1.0)
+            mat(p + "mix.o", E, inner)
+        else:
+            H, dn, dr, dv, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            mat(p + "mix.q", H * (dn + dr), E, q_gain * E ** -0.5)
+            mat(p + "mix.dkv", r + dr, E)
+            vec(p + "mix.dkv.norm", r, 1.0)
+            mat(p + "mix.uk", H * dn, r)
+            mat(p + "mix.uv", H * dv, r)
+            vec(p + "mix.sink", H, 0.0 if sink is None else sink, 0.5)
+            mat(p + "mix.g", H * dv, E)
+            mat(p + "mix.o", E, H * dv)
+        if ly["mlp"]:
+            ml = ly["mlp"]
+            mat(p + "rg2", E, E)
+            vec(p + "rg2.b", E)
+            mat(p + "mlp.router", ml["router"]["experts"], E, 1.0)  # wide logits: no near ties between experts
+            vec(p + "mlp.router.b", ml["router"]["experts"])
+            for e in range(ml["router"]["experts"]):
+                mat(p + "mlp.e%d.gate" % e, ml["expert"]["ff"], E)
+                mat(p + "mlp.e%d.up" % e, ml["expert"]["ff"], E)
+                mat(p + "mlp.e%d.down" % e, E, ml["expert"]["ff"])
+            if ml["shared"]:
+                sf = ml["shared"]["ff"]
+                mat(p + "mlp.shared.gate", sf, E)
+                mat(p + "mlp.shared.up", sf, E)
+                mat(p + "mlp.shared.down", E, sf)
+                mat(p + "mlp.shared.sg", 1, E)
+    return W
+
+
+def bits(t):
+    return (t.contiguous().view(torch.int32).numpy().astype(np.uint32) >> 16).astype(np.uint16)
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = kf.Context(0)
+    yield c
+    c.close()
+
+
+def build(ctx, cfg, W, f32, max_seq=256, slots=2, panel=64, logit_rows=None):
+    gpt = {"max_seq_len": max_seq, "max_batch": slots, "max_prefill": panel, "logit_rows": logit_rows or panel}
+    if f32:
+        gpt["compute_dtype"] = "float32"
+    m = kf.Model(ctx, {"hf_config": cfg, "gpt": gpt})
+    assert sorted(m.tensor_names()) == sorted(W.keys())
+    for k, v in W.items():
+        m.set_tensor(k, bits(v))
+    return m
+
+
+def rel(got, want, q=1.0):
+    """largest (q = 1) or q-quantile row error: rms of the difference, mean removed, over the rms of the wanted logits"""
+    d = np.asarray(got, dtype=np.float64) - np.asarray(want, dtype=np.float64)
+    d = d - d.mean(-1, keepdims=True)
+    w = np.asarray(want, dtype=np.float64)
+    w = w - w.mean(-1, keepdims=True)
+    return float(np.quantile(np.atleast_1d(np.sqrt((d ** 2).mean(-1))), q) / np.sqrt((w ** 2).mean()))
+
+
+def close(got, want, f32):
+    """float32: every row within 2e-4.  bf16: nine rows in ten within 6e-2 and none beyond 0.5 -- the bf16 rounding of a router's input
+    may move a token to another expert where two logits are close, which the strict float32 runs of the same case rule out as a fault."""
+    if f32:
+        return rel(got, want) < TOL[True]
+    return rel(got, want, 0.9) < TOL[False] and rel(got, want) < 0.5
+
+
+def oracle(cfg, W, toks):
+    return ref.forward(cfg, W, list(toks)).numpy()
+
+
+def run_cut(model, toks, cuts, slot=0):
+    """feed toks in portions of the given sizes (the rest one by one); fp32 logits of every position"""
+    out, at = [], 0
+    sizes = list(cuts)
+    while at < len(toks):
+        n = sizes.pop(0) if sizes else 1
+        n = min(n, len(toks) - at)
+        lg, _ = model.forward_rows(toks[at:at + n], at, slot=slot, rows=list(range(n)))
+        out.append(lg)
+        at += n
+    return np.concatenate(out)
+
+
+def tokens(n, vocab, seed):
+    return np.random.RandomState(seed).randint(0, vocab, n).tolist()
+
+
+FULL = [(ssm(), moe()), (att(), moe(shared=0)), (ssm(heads=4, vdim=6, state=5, groups=1, norm_groups=1, conv=2), None), (att(heads=2, dim=8, rot_dim=8, rot_dims=8, vdim=8, kv_rank=24), moe(experts=3, top=3, ff=16, shared=8))]
+
+
+# ------------------------------------------------------------------------------------------------------------ each mechanism alone
+@pytest.mark.parametrize("f32", [True, False])
+@pytest.mark.parametrize("layer", [
+    (ssm(), None),
+    (ssm(heads=4, vdim=16, state=16, groups=4, norm_groups=4, conv=1), None),        # groups == heads, one tap (no convolution tail)
+    (ssm(heads=2, vdim=40, state=70, groups=1, norm_groups=1, conv=3), None),        # state spread over several lanes, not a multiple of 16
+    (att(), None),
+    (att(heads=1, dim=8, rot_dim=4, rot_dims=4, vdim=8, kv_rank=8), None),           # one head, all sizes small and equal
+    (att(heads=5, dim=24, rot_dim=16, rot_dims=6, vdim=10, kv_rank=72, base=1e6), None),
+    (ssm(heads=1, vdim=8, state=8, groups=1), moe(experts=4, top=1, ff=8, shared=0)),  # top 1: the weight is exactly 1
+    (ssm(heads=1, vdim=8, state=8, groups=1), moe(experts=1, top=1, ff=20, shared=12)),
+    (ssm(heads=1, vdim=8, state=8, groups=1), moe(experts=6, top=6, ff=12, shared=16)),  # every expert chosen
+], ids=["ssm", "ssm_g_eq_h_conv1", "ssm_wide_state", "attn", "attn_one_head", "attn_partial_rot", "moe_top1", "moe_one_expert", "moe_all"])
+def test_single_layer_prompt(ctx, layer, f32):
+    cfg = config([layer], width=32, groups=4)
+    W = weights(cfg, seed=3)
+    toks = tokens(37, cfg["vocab"], 1)
+    m = build(ctx, cfg, W, f32)
+    got, _ = m.forward_rows(toks, 0, rows=list(range(len(toks))))
+    assert close(got, oracle(cfg, W, toks), f32)
+    m.close()
+
+
+def test_general_matmul_shapes(ctx):
+    """kf_linear_g / kf_linear_g_swiglu on shapes the tuned kernels refuse and on one they take, few rows (GEMV) and many (tiles)"""
+    import ctypes as C
+    rs = np.random.RandomState(0)
+    for (M, N, K) in [(1, 7, 5), (3, 50, 33), (16, 24, 64), (17, 130, 96), (100, 1, 48), (70, 144, 256), (5, 32, 128), (40, 64, 256)]:
+        w = bf16_grid(torch.from_numpy(rs.randn(N, K).astype(np.float32)))
+        w2 = bf16_grid(torch.from_numpy(rs.randn(N, K).astype(np.float32)))
+        x = bf16_grid(torch.from_numpy(rs.randn(M, K).astype(np.float32)))
+        wd, w2d = ctx.array(bits(w)), ctx.array(bits(w2))
+        want = (x.double() @ w.double().T).numpy()
+        z = x.double() @ w.double().T
+        want2 = (z * torch.sigmoid(z) * (x.double() @ w2.double().T)).numpy()
+        for act_f32 in (0, 1):
+            xd = ctx.array(x.numpy() if act_f32 else bits(x))
+            y = ctx.empty(M * N * 4)
+            d = kf.TensorDesc(wd.ptr, None, N, K, kf.KF_T_BF16, 128, 0, None, None)
+            d2 = kf.TensorDesc(w2d.ptr, None, N, K, kf.KF_T_BF16, 128, 0, None, None)
+            ctx.check(ctx.lib.kf_linear_g(ctx.h, y.ptr, N, C.byref(d), xd.ptr, act_f32, K, M), "kf_linear_g")
+            got = y.numpy(np.float32, (M, N))
+            assert np.abs(got - want).max() <= 2e-5 * np.abs(want).max() + 1e-6, (M, N, K, act_f32)
+            ctx.check(ctx.lib.kf_linear_g_swiglu(ctx.h, y.ptr, N, C.byref(d), C.byref(d2), xd.ptr, act_f32, K, M), "kf_linear_g_swiglu")
+            if act_f32:
+                got2 = y.numpy(np.float32, (M, N))
+                assert np.abs(got2 - want2).max() <= 2e-5 * np.abs(want2).max() + 1e-6
+            else:
+                got2 = (y.numpy(np.uint16, count=M * N).astype(np.uint32) << 16).view(np.float32).reshape(M, N)
+                assert np.abs(got2 - want2).max() <= 5e-3 * np.abs(want2).max() + 1e-6
+
+
+# ------------------------------------------------------------------------------------------------------------ whole stacks
+@pytest.mark.parametrize("f32", [True, False])
+def test_stack_prompt_and_decode(ctx, f32):
+    """a prompt in one step, then token by token: both equal the oracle; the first tokens of a sequence decoded one by one as well"""
+    cfg = config(FULL)
+    W = weights(cfg, seed=5)
+    toks = tokens(90, cfg["vocab"], 2)
+    want = oracle(cfg, W, toks)
+    m = build(ctx, cfg, W, f32)
+    assert close(run_cut(m, toks, [64, 26]), want, f32)          # two panels
+    assert close(run_cut(m, toks, [50]), want, f32)              # 50 at once, 40 decoded (graph replay from the second step on)
+    assert close(run_cut(m, toks[:12], []), want[:12], f32)       # from the very first token one by one
+    m.close()
+
+
+def test_portions_of_many_sizes(ctx):
+    cfg = config(FULL)
+    W = weights(cfg, seed=6)
+    toks = tokens(131, cfg["vocab"], 3)
+    want = oracle(cfg, W, toks)
+    m = build(ctx, cfg, W, True)
+    for cuts in ([2, 2, 3, 2, 64, 2, 31, 2, 17], [1, 2, 1, 63, 64, 1], [7] * 19, [64, 64, 2], [3, 1, 1, 2, 5, 64, 2, 2, 2, 40]):
+        assert rel(run_cut(m, toks, cuts), want) < TOL[True], cuts
+    m.close()
+
+
+def test_slots_reused_and_interleaved(ctx):
+    """two requests advance alternately in two slots; a released slot is taken by a new request and nothing of the old one shows"""
+    cfg = config(FULL)
+    W = weights(cfg, seed=7)
+    a, b, c = tokens(70, cfg["vocab"], 4), tokens(45, cfg["vocab"], 5), tokens(20, cfg["vocab"], 6)
+    wa, wb, wc = oracle(cfg, W, a), oracle(cfg, W, b), oracle(cfg, W, c)
+    m = build(ctx, cfg, W, True, slots=2)
+    sa, sb = m.acquire_slot(), m.acquire_slot()
+    assert {sa, sb} == {0, 1}
+    with pytest.raises(kf.KoifishError):
+        m.acquire_slot()
+    ga, gb, ia, ib = [], [], 0, 0
+    for na, nb in [(30, 2), (1, 20), (2, 1), (37, 22)]:
+        lg, _ = m.forward_rows(a[ia:ia + na], ia, slot=sa, rows=list(range(na)))
+        ga.append(lg), (ia := ia + na)
+        lg, _ = m.forward_rows(b[ib:ib + nb], ib, slot=sb, rows=list(range(nb)))
+        gb.append(lg), (ib := ib + nb)
+    assert rel(np.concatenate(ga), wa) < TOL[True] and rel(np.concatenate(gb), wb) < TOL[True]
+    m.release_slot(sa)
+    with pytest.raises(kf.KoifishError):
+        m.release_slot(sa)
+    sc = m.acquire_slot()
+    assert sc == sa  # the slot that held the 70-token request, state and rows still in place
+    assert rel(run_cut(m, c, [3, 2], slot=sc), wc) < TOL[True]
+    m.close()
+
+
+def test_batched_decode_of_unequal_requests(ctx):
+    """three sequences of different lengths take one token each in one step: every row equals the sequence run alone"""
+    cfg = config(FULL)
+    W = weights(cfg, seed=8)
+    seqs = [tokens(n, cfg["vocab"], 10 + n) for n in (41, 7, 18)]
+    m = build(ctx, cfg, W, True, slots=3)
+    for s, t in enumerate(seqs):
+        m.forward_rows(t[:-4], 0, slot=s)
+    for k in range(4, 0, -1):
+        lg, _ = m.forward_batch([t[len(t) - k] for t in seqs], [len(t) - k for t in seqs])
+        for s, t in enumerate(seqs):
+            assert rel(lg[s], oracle(cfg, W, t)[len(t) - k]) < TOL[True], (s, k)
+    m.close()
+
+
+# ------------------------------------------------------------------------------------------------------------ shaped weights
+@pytest.mark.parametrize("f32", [True, False])
+def test_far_keys_edges_and_sink(ctx, f32):
+    """peaked softmax over 600 positions (queries x 6), large sinks: the key that wins is anywhere, often far back; a mask that is one
+    position off, a lost first token or a sink left out moves the logits by tens of percent.  Prompt panels and decoded tokens."""
+    cfg = config([(att(heads=3, dim=16, rot_dim=8, rot_dims=8, vdim=12, kv_rank=40, base=1e4), None), (att(), moe())])
+    W = weights(cfg, seed=9, q_gain=6.0, sink=2.5)
+    toks = tokens(600, cfg["vocab"], 7)
+    want = oracle(cfg, W, toks)
+    # the shaping works: without the sink, or seeing one key less, the oracle itself moves far beyond the gate
+    W2 = dict(W)
+    for k in W:
+        if k.endswith("mix.sink"):
+            W2[k] = W[k] - 30.0
+    assert rel(oracle(cfg, W2, toks), want) > 10 * TOL[f32]
+    m = build(ctx, cfg, W, f32, max_seq=640)
+    got = run_cut(m, toks, [64] * 8 + [2, 2, 3, 29])  # 512 in panels, small portions up to 548, then 52 decoded
+    assert close(got, want, f32)
+    m.close()
+
+
+def test_slow_decay_keeps_the_first_tokens(ctx):
+    """decays close to 1 (A_log = -6): the state after 300 tokens still holds the first ones; cutting the sequence anywhere, also inside
+    the convolution's reach of a cut, leaves the logits alone"""
+    cfg = config([(ssm(heads=2, vdim=8, state=12, groups=2, norm_groups=1, conv=4), None), (ssm(heads=3, vdim=8, state=20, groups=1, conv=3), moe(experts=4, top=2, ff=8))])
+    W = weights(cfg, seed=10, a_log=-6.0)
+    toks = tokens(300, cfg["vocab"], 8)
+    want = oracle(cfg, W, toks)
+    other = list(toks)
+    other[0] = (toks[0] + 1) % cfg["vocab"]
+    assert rel(oracle(cfg, W, other)[-1], want[-1]) > 10 * TOL[True]  # the last logits do depend on the first token
+    m = build(ctx, cfg, W, True, max_seq=320)
+    assert rel(run_cut(m, toks, [64, 64, 1, 2, 1, 1, 3, 64, 2]), want) < TOL[True]  # ... then 98 decoded one by one
+    m.close()
+
+
+# ------------------------------------------------------------------------------------------------------------ entry points
+def test_greedy_generation(ctx):
+    cfg = config(FULL)
+    W = weights(cfg, seed=11)
+    prompt = tokens(70, cfg["vocab"], 9)  # longer than a panel
+    seq = list(prompt)
+    for _ in range(12):
+        seq.append(int(np.argmax(oracle(cfg, W, seq)[-1])))
+    m = build(ctx, cfg, W, True)
+    out, why = m.generate(prompt, 12)
+    assert out == seq[len(prompt):] and why == 2
+    m.close()
+
+
+def test_command_line_on_a_checkpoint_folder(ctx, tmp_path):
+    """config.json + model.safetensors on disk -> `generate` and `trace` of the command line, both number formats"""
+    cfg = config(FULL[:2])
+    W = weights(cfg, seed=12)
+    d = tmp_path / "ckpt"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(cfg))
+    write_safetensors(str(d / "model.safetensors"), [(k, "BF16", bits(v).reshape(v.shape)) for k, v in W.items()])
+    a, b = tokens(75, cfg["vocab"], 13), tokens(9, cfg["vocab"], 14)
+    wa, wb = oracle(cfg, W, a), oracle(cfg, W, b)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": a[:70], "want": [0, 5, 69]}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": a[70:72], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "x", "tokens": a[72:], "want": [2, 1]}], "end": ["x"]},
+             {"step": 3, "entries": [{"id": "y", "tokens": b, "want": [8]}], "end": ["y"]}]
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    for dtype in ("float32", "bfloat16"):
+        out = tmp_path / ("out_" + dtype)
+        r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", str(d), "--dtype", dtype, "--out", str(out), "--max-tokens", "128"],
+                           input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, env=env, timeout=900)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+        assert not (out / "1.f32").exists()
+        f = lambda n: np.fromfile(str(out / ("%d.f32" % n)), dtype="<f4").reshape(-1, cfg["vocab"])
+        assert close(np.concatenate([f(0), f(2), f(3)]), np.concatenate([wa[[0, 5, 69]], wa[[74, 73]], wb[[8]]]), dtype == "float32")
+    r = subprocess.run([sys.executable, "-m", "koifish_b200.cli", "generate", "--model", str(d), "--ids", ",".join(map(str, b)), "--max-new-tokens", "5"],
+                       capture_output=True, text=True, env=env, cwd=ROOT, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    seq = list(b)
+    for _ in range(5):
+        seq.append(int(np.argmax(oracle(cfg, W, seq)[-1])))
+    got = json.loads(r.stdout.strip().splitlines()[-1])["tokens"]
+    assert len(got) == 5 and got[0] == seq[len(b)]  # bf16 serving: the first token is far from a tie; later ones may legitimately differ
