@@ -6,7 +6,7 @@
 //     contiguous (offsets[e] .. offsets[e+1]) and may gather their input row through src_row;
 //   * DUAL form: two weight tables A, B of equal shape and y = silu(A x) * (B x), the gate / up pair of a gated feed-forward.
 // Two kernels: a warp-per-output GEMV for a handful of rows (decode: every weight row is read once, 16-byte loads when the row length
-// allows) and a 64 x 64 x 16 shared-memory tile kernel for panels (mma.sync m16n8k16 for bf16 activations, FFMA for float ones).
+// allows) and a 64 x 64 x 32 shared-memory tile kernel for panels (mma.sync m16n8k16 for bf16 activations, FFMA for float ones).
 // No reference equivalent: the reference's SLP::Forw hands every shape to cuBLASLt (src/Device/CUDA/NeuronFuse.cu:305-381).
 #include "kf_common.cuh"
 
@@ -92,15 +92,36 @@ __global__ void __launch_bounds__(256) kf_lin_gemv_kernel(LinArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------------------------------ tile kernel
-// 64 slots x 64 outputs per CTA, k in steps of 16; 256 threads.  Float activations: each thread a 4 x 4 block of FFMA accumulators.
-// bf16 activations: 8 warps as 4 (m) x 2 (n), each warp 16 x 32 through four mma.sync.m16n8k16 per k step; operands converted from the
-// same shared tiles.  Every load is bounds-checked, so M, N and K are free.
-constexpr int BM = 64, BN = 64, BK = 16;
+// 64 slots x 64 outputs per CTA, k in steps of 32; 256 threads.  Float activations: each thread a 4 x 4 block of FFMA accumulators.
+// bf16 activations: 8 warps as 4 (m) x 2 (n), each warp 16 x 32 through mma.sync.m16n8k16; operands come from the same shared tiles.
+// The next k step's operands are fetched into registers (16-byte loads when the row length and alignment allow, else element by
+// element) while the current one is multiplied.  Every load is bounds-checked, so M, N and K are free.
+constexpr int BM = 64, BN = 64, BK = 32;
 
 __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, const uint32_t* b) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// 8 consecutive k of one row: thread t fetches row t / 4, k offset (t % 4) * 8
+template <typename T>
+struct __align__(16) Frag8 {
+    T v[8];
+};
+template <typename T>
+__device__ __forceinline__ void fetch8(Frag8<T>& f, const T* base, size_t row_off, int k, int K, bool row_ok, bool vec) {
+    if (row_ok && vec && k + 8 <= K) {
+        if (sizeof(T) == 2) {
+            *reinterpret_cast<uint4*>(f.v) = *reinterpret_cast<const uint4*>(base + row_off + k);
+        } else {
+            *reinterpret_cast<float4*>(f.v)     = *reinterpret_cast<const float4*>(base + row_off + k);
+            *reinterpret_cast<float4*>(f.v + 4) = *reinterpret_cast<const float4*>(base + row_off + k + 4);
+        }
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) f.v[j] = (row_ok && k + j < K) ? base[row_off + k + j] : T(0);
 }
 
 template <typename TA, bool DUAL>
@@ -114,17 +135,21 @@ __global__ void __launch_bounds__(256) kf_lin_tile_kernel(LinArgs a) {
     const uint16_t* W0 = a.Wt0 ? a.Wt0[g] : a.W0;
     const uint16_t* W1 = DUAL ? (a.Wt1 ? a.Wt1[g] : a.W1) : nullptr;
     constexpr bool MMA = sizeof(TA) == 2;
-    // shared tiles, k-major rows padded against bank conflicts
-    __shared__ TA sx[BM][BK + (MMA ? 8 : 1)];
-    __shared__ uint16_t sw0[BN][BK + 8];
-    __shared__ uint16_t sw1[DUAL ? BN : 1][BK + 8];
-    __shared__ int srow[BM];
+    constexpr int LDS = BK + 8;  // row pitch in elements: 16-byte aligned rows, conflict-free fragment loads
+    __shared__ __align__(16) TA sx[BM][LDS];
+    __shared__ __align__(16) uint16_t sw0[BN][LDS];
+    __shared__ __align__(16) uint16_t sw1[DUAL ? BN : 1][LDS];
     const int tid = threadIdx.x;
-    if (tid < BM) {
-        const int s = m0 + tid;
-        srow[tid]   = s < hi ? (a.src_row ? a.src_row[s] : s) : -1;
+    const int lr = tid >> 2, lk = (tid & 3) * 8;  // this thread's load: row lr, k offset lk
+    int xrow = -1;
+    {
+        const int s = m0 + lr;
+        if (s < hi) xrow = a.src_row ? a.src_row[s] : s;
     }
-    __syncthreads();
+    const bool wok = n0 + lr < a.N;
+    const size_t xoff = (size_t)(xrow < 0 ? 0 : xrow) * a.ldx, woff = (size_t)(n0 + lr) * a.K;
+    const bool xvec = (a.ldx % 8 == 0) && (((uintptr_t)a.x & 15) == 0) && (a.K % 8 == 0);
+    const bool wvec = (a.K % 8 == 0) && (((uintptr_t)W0 & 15) == 0) && (!DUAL || ((uintptr_t)W1 & 15) == 0);
     float acc0[16], acc1[DUAL ? 16 : 1];
 #pragma unroll
     for (int i = 0; i < 16; i++) acc0[i] = 0.f;
@@ -134,52 +159,49 @@ __global__ void __launch_bounds__(256) kf_lin_tile_kernel(LinArgs a) {
     const int warp = tid >> 5, lane = tid & 31;
     const int wm = warp & 3, wn = warp >> 2;      // MMA: warp tile rows wm*16, cols wn*32
     const int tr = tid >> 4, tc = tid & 15;        // FFMA: thread rows tr*4.., cols tc*4..
+    Frag8<TA> fx;
+    Frag8<uint16_t> fw0, fw1;
+    fetch8<TA>(fx, (const TA*)a.x, xoff, lk, a.K, xrow >= 0, xvec);
+    fetch8<uint16_t>(fw0, W0, woff, lk, a.K, wok, wvec);
+    if (DUAL) fetch8<uint16_t>(fw1, W1, woff, lk, a.K, wok, wvec);
     for (int k0 = 0; k0 < a.K; k0 += BK) {
-        // stage x: 64 x 16 elements, 4 per thread
-        {
-            const int r = tid >> 2, c = (tid & 3) * 4;
-            const int row = srow[r];
+        __syncthreads();  // the previous step's fragments have been read
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int k = k0 + c + j;
-                TA v = TA(0);
-                if (row >= 0 && k < a.K) v = ((const TA*)a.x)[(size_t)row * a.ldx + k];
-                sx[r][c + j] = v;
-            }
-            const int n = n0 + r;
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int k = k0 + c + j;
-                const bool ok = n < a.N && k < a.K;
-                sw0[r][c + j] = ok ? W0[(size_t)n * a.K + k] : (uint16_t)0;
-                if (DUAL) sw1[r][c + j] = ok ? W1[(size_t)n * a.K + k] : (uint16_t)0;
-            }
-        }
+        for (int j = 0; j < 8; j++) sx[lr][lk + j] = fx.v[j];
+        *reinterpret_cast<uint4*>(&sw0[lr][lk]) = *reinterpret_cast<const uint4*>(fw0.v);
+        if (DUAL) *reinterpret_cast<uint4*>(&sw1[lr][lk]) = *reinterpret_cast<const uint4*>(fw1.v);
         __syncthreads();
+        if (k0 + BK < a.K) {  // next step's operands travel while this one is multiplied
+            fetch8<TA>(fx, (const TA*)a.x, xoff, k0 + BK + lk, a.K, xrow >= 0, xvec);
+            fetch8<uint16_t>(fw0, W0, woff, k0 + BK + lk, a.K, wok, wvec);
+            if (DUAL) fetch8<uint16_t>(fw1, W1, woff, k0 + BK + lk, a.K, wok, wvec);
+        }
         if (MMA) {
             const int gr = lane >> 2, tg = lane & 3;
-            uint32_t af[4];
             const uint16_t* xa = (const uint16_t*)&sx[wm * 16][0];
-            const int ldsx = BK + 8;
-            af[0] = *reinterpret_cast<const uint32_t*>(xa + (gr)*ldsx + tg * 2);
-            af[1] = *reinterpret_cast<const uint32_t*>(xa + (gr + 8) * ldsx + tg * 2);
-            af[2] = *reinterpret_cast<const uint32_t*>(xa + (gr)*ldsx + tg * 2 + 8);
-            af[3] = *reinterpret_cast<const uint32_t*>(xa + (gr + 8) * ldsx + tg * 2 + 8);
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int nr = wn * 32 + j * 8 + gr;
-                uint32_t bf[2];
-                bf[0] = *reinterpret_cast<const uint32_t*>(&sw0[nr][tg * 2]);
-                bf[1] = *reinterpret_cast<const uint32_t*>(&sw0[nr][tg * 2 + 8]);
-                mma_bf16_16816(&acc0[j * 4], af, bf);
-                if (DUAL) {
-                    bf[0] = *reinterpret_cast<const uint32_t*>(&sw1[nr][tg * 2]);
-                    bf[1] = *reinterpret_cast<const uint32_t*>(&sw1[nr][tg * 2 + 8]);
-                    mma_bf16_16816(&acc1[j * 4], af, bf);
+            for (int kk = 0; kk < BK; kk += 16) {
+                uint32_t af[4];
+                af[0] = *reinterpret_cast<const uint32_t*>(xa + (gr)*LDS + kk + tg * 2);
+                af[1] = *reinterpret_cast<const uint32_t*>(xa + (gr + 8) * LDS + kk + tg * 2);
+                af[2] = *reinterpret_cast<const uint32_t*>(xa + (gr)*LDS + kk + tg * 2 + 8);
+                af[3] = *reinterpret_cast<const uint32_t*>(xa + (gr + 8) * LDS + kk + tg * 2 + 8);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int nr = wn * 32 + j * 8 + gr;
+                    uint32_t bf[2];
+                    bf[0] = *reinterpret_cast<const uint32_t*>(&sw0[nr][kk + tg * 2]);
+                    bf[1] = *reinterpret_cast<const uint32_t*>(&sw0[nr][kk + tg * 2 + 8]);
+                    mma_bf16_16816(&acc0[j * 4], af, bf);
+                    if (DUAL) {
+                        bf[0] = *reinterpret_cast<const uint32_t*>(&sw1[nr][kk + tg * 2]);
+                        bf[1] = *reinterpret_cast<const uint32_t*>(&sw1[nr][kk + tg * 2 + 8]);
+                        mma_bf16_16816(&acc1[j * 4], af, bf);
+                    }
                 }
             }
         } else {
-#pragma unroll
+#pragma unroll 8
             for (int k = 0; k < BK; k++) {
                 float xv[4], wv[4], uv[4];
 #pragma unroll
@@ -198,7 +220,6 @@ __global__ void __launch_bounds__(256) kf_lin_tile_kernel(LinArgs a) {
                     }
             }
         }
-        __syncthreads();
     }
     auto store = [&](int r, int n, float v0, float v1) {
         const int s = m0 + r;

@@ -167,34 +167,47 @@ __global__ void __launch_bounds__(256) kf_latent_append_kernel(TC* __restrict__ 
         put(rank + i, v);
     }
 }
-// q' [M][H][rank + rot_dim] = scale * [ W_uk[h]^T q_plain[h]  |  rotate(q_rot[h]) ]; one block per (token, head)
+// q' [M][H][rank + rot_dim] = scale * [ W_uk[h]^T q_plain[h]  |  rotate(q_rot[h]) ]; one block per (QT tokens, head): a weight element
+// read once serves QT tokens
+constexpr int QT = 8;
 __global__ void __launch_bounds__(128) kf_latent_query_kernel(float* __restrict__ qa, const float* __restrict__ q, int ldq, const uint16_t* __restrict__ Wuk,
-                                                              const float* __restrict__ inv_freq, const int32_t* __restrict__ pos, int H, int dn, int rot_dim,
-                                                              int dims, int rank, float scale) {
-    extern __shared__ float sq[];  // [dn + rot_dim]
-    const int m = blockIdx.x, h = blockIdx.y, D = dn + rot_dim;
-    const float* qh = q + (size_t)m * ldq + (size_t)h * D;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) sq[i] = qh[i];
+                                                              const float* __restrict__ inv_freq, const int32_t* __restrict__ pos, int M, int H, int dn,
+                                                              int rot_dim, int dims, int rank, float scale) {
+    extern __shared__ float sq[];  // [QT][dn + rot_dim]
+    const int m0 = blockIdx.x * QT, h = blockIdx.y, D = dn + rot_dim, W = rank + rot_dim;
+    const int nt = min(QT, M - m0);
+    for (int i = threadIdx.x; i < nt * D; i += blockDim.x) {
+        const int t = i / D, d = i - t * D;
+        sq[t * D + d] = q[(size_t)(m0 + t) * ldq + (size_t)h * D + d];
+    }
     __syncthreads();
-    float* o = qa + ((size_t)m * H + h) * (rank + rot_dim);
     for (int c = threadIdx.x; c < rank; c += blockDim.x) {
-        float s = 0.f;
-        for (int d = 0; d < dn; d++) s = fmaf(sq[d], bf16_bits_to_f32(Wuk[((size_t)h * dn + d) * rank + c]), s);
-        o[c] = s * scale;
+        float s[QT];
+#pragma unroll
+        for (int t = 0; t < QT; t++) s[t] = 0.f;
+        for (int d = 0; d < dn; d++) {
+            const float w = bf16_bits_to_f32(Wuk[((size_t)h * dn + d) * rank + c]);
+#pragma unroll
+            for (int t = 0; t < QT; t++) s[t] = fmaf(sq[(t < nt ? t : 0) * D + d], w, s[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < QT; t++)
+            if (t < nt) qa[((size_t)(m0 + t) * H + h) * W + c] = s[t] * scale;
     }
     const int half = dims / 2;
-    const float fp = (float)pos[m];
-    for (int i = threadIdx.x; i < rot_dim; i += blockDim.x) {
-        float v = sq[dn + i];
-        if (i < dims) {
-            const int j = i < half ? i : i - half;
-            const float ang = fp * inv_freq[j];
+    for (int i = threadIdx.x; i < nt * rot_dim; i += blockDim.x) {
+        const int t = i / rot_dim, e = i - t * rot_dim;
+        const float* sr = sq + t * D + dn;
+        float v = sr[e];
+        if (e < dims) {
+            const int j = e < half ? e : e - half;
+            const float ang = (float)pos[m0 + t] * inv_freq[j];
             double sn, cs;
             sincos((double)ang, &sn, &cs);
-            const float a = sq[dn + j], b = sq[dn + j + half];
-            v = i < half ? a * (float)cs - b * (float)sn : b * (float)cs + a * (float)sn;
+            const float a = sr[j], b = sr[j + half];
+            v = e < half ? a * (float)cs - b * (float)sn : b * (float)cs + a * (float)sn;
         }
-        o[rank + i] = v * scale;
+        qa[((size_t)(m0 + t) * H + h) * W + rank + e] = v * scale;
     }
 }
 // One block (4 warps) per (token, head): warp w takes keys w, w + 4, ...; a lane owns elements lane, lane + 32, ... of a row.  Online
@@ -335,9 +348,9 @@ extern "C" int kf_latent_attention(kf_ctx* ctx, float* lat_out, float* qa_work, 
                                    const int32_t* slot_dev, int M, int H, int dn, int rot_dim, int rot_dims, int rank, float scale) {
     if (!ctx || !lat_out || !qa_work || !q || !w_uk_bf16 || !sink_bf16 || !cache || !inv_freq_dev || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, M >= 1 && H >= 1 && dn >= 1 && rank >= 1 && rank + rot_dim <= 32 * LMAX && rot_dims <= rot_dim && rot_dims % 2 == 0, "rank + rot_dim <= 640");
-    dim3 grid(M, H);
-    kf_latent_query_kernel<<<grid, 128, (size_t)(dn + rot_dim) * 4, ctx->stream>>>(qa_work, q, ldq, (const uint16_t*)w_uk_bf16, inv_freq_dev, pos_dev, H, dn,
-                                                                                 rot_dim, rot_dims, rank, scale);
+    dim3 grid(M, H), qgrid((M + QT - 1) / QT, H);
+    kf_latent_query_kernel<<<qgrid, 128, (size_t)QT * (dn + rot_dim) * 4, ctx->stream>>>(qa_work, q, ldq, (const uint16_t*)w_uk_bf16, inv_freq_dev, pos_dev, M,
+                                                                                       H, dn, rot_dim, rot_dims, rank, scale);
     KF_LAUNCH_CHECK(ctx);
     const size_t smem = (size_t)(4 * rank + 8) * 4;
     if (cache_f32)
