@@ -109,7 +109,7 @@ SIGNATURES = {
     "kf_conv_silu": (_I, [_P, _P, _P, _I, _I, _P, _P, _P, _SZ, _P, _P, _I, _I, _I, _I]),
     "kf_ssm_scan": (_I, [_P, _P, _I, _P, _P, _I, _I, _P, _P, _P, _P, _SZ, _P, _P, _I, _I, _I, _I, _I, _I]),
     "kf_latent_append": (_I, [_P, _P, _I, _SZ, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F]),
-    "kf_latent_attention": (_I, [_P, _P, _P, _P, _I, _P, _P, _P, _I, _SZ, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F]),
+    "kf_latent_attention": (_I, [_P, _P, _P, _P, _I, _P, _P, _P, _I, _SZ, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I]),
     "kf_latent_expand": (_I, [_P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I]),
     "kf_nccl_unique_id": (_I, [_P]),
     "kf_ctx_init_nccl": (_I, [_P, _P, _I, _I]),

@@ -28,7 +28,7 @@ __global__ void kf_conv_silu_kernel(float* __restrict__ out, const float* __rest
     const int m = blockIdx.x, seq = m / T, t = m - seq * T;
     const int p = pos[m];
     const float* tl = tail + (size_t)slot[m] * tail_stride;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
         float s = b ? bf16_bits_to_f32(b[c]) : 0.f;
         for (int j = 0; j < K; j++) {
             const int back = K - 1 - j;
@@ -47,7 +47,7 @@ __global__ void kf_conv_tail_kernel(float* __restrict__ tail, size_t tail_stride
     const int seq = blockIdx.x, m0 = seq * T;
     float* tl = tail + (size_t)slot[m0] * tail_stride;
     const int p0 = pos[m0];
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
         for (int i = 0; i < K - 1; i++) {
             const int t = T - (K - 1) + i;  // panel-relative index of the input that lands in tail[i]
             float v;
@@ -270,6 +270,208 @@ __global__ void __launch_bounds__(128) kf_latent_attn_kernel(float* __restrict__
         o[e] = v / den;
     }
 }
+// ---- the same attention on tensor cores (bf16 cache rows; rank and rank + rot_dim multiples of 8) --------------------------------------
+// One CTA (4 warps) per (token, group of 16 heads, key split).  The 16 heads of a token are the 16 rows of an m16n8k16 tile and share
+// every cached row, so a row is fetched once per 16 heads.  Per block of 16 keys, staged in shared memory with cp.async (two buffers):
+//   scores  S[16 x 16] = Q'[16 x W] C^T : the W/16 k-steps are dealt round-robin to the 4 warps, partial tiles summed through shared memory;
+//   softmax online in fp32, every warp alike (rows gr and gr + 8 of a lane's fragment, quad shuffles);
+//   values  O[16 x rank] += P C[:, :rank] : warp w owns a quarter of the rank; the fp32 weights P enter the bf16 tensor-core product as
+//           hi + lo (two mma per tile), which keeps 16 bits of each weight.
+// Splits write (O, max, sum) to a workspace; kf_latent_merge_kernel combines them and adds the sink term to the denominator.
+constexpr int KSW = 10;   // k-steps of 16 per warp: W <= 640
+constexpr int NTW = 16;   // value n-tiles of 8 per warp: rank <= 512
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory"); }
+
+__global__ void __launch_bounds__(128) kf_latent_attn_mma_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, const float* __restrict__ qa,
+                                                                 const uint16_t* __restrict__ cache, size_t slot_stride, const int32_t* __restrict__ pos,
+                                                                 const int32_t* __restrict__ slot, int H, int HG, int rank, int rot_dim, int S) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int W = rank + rot_dim, W16 = (W + 15) & ~15, LD = W16 + 8;  // row pitch in bf16 elements (16-byte multiple, 4-bank skew)
+    uint16_t* sQ  = (uint16_t*)smraw;                 // [16][LD]
+    uint16_t* sK0 = sQ + 16 * LD;                     // two key tiles [16][LD]
+    float* sS     = (float*)(sK0 + 2 * 16 * LD);      // [4 warps][2 n-tiles][32 lanes][4]
+    const int m = blockIdx.x, hg = blockIdx.y, sp = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gr = lane >> 2, tg = lane & 3;
+    const int last = pos[m];
+    const int nblk = (last + 16) / 16;                 // key blocks covering 0 .. last
+    const int per  = (nblk + S - 1) / S;
+    const int b_lo = sp * per, b_hi = min(nblk, b_lo + per);
+    const uint16_t* base = cache + (size_t)slot[m] * slot_stride;
+    // queries of this head group as bf16, zero rows beyond H and zero columns beyond W; zero the pad columns of both key tiles
+    for (int i = tid; i < 16 * W16; i += 128) {
+        const int r = i / W16, c = i - r * W16, h = hg * 16 + r;
+        sQ[r * LD + c] = (h < H && c < W) ? f32_to_bf16_bits(qa[((size_t)m * H + h) * W + c]) : (uint16_t)0;
+    }
+    for (int i = tid; i < 2 * 16 * (W16 - W); i += 128) {
+        const int r = i / (W16 - W), c = W + i - r * (W16 - W);
+        sK0[r * LD + c] = 0;
+    }
+    const int chunks = W / 8;  // 16-byte pieces per row
+    auto stage = [&](int blk, int buf) {
+        uint16_t* dst = sK0 + buf * 16 * LD;
+        for (int i = tid; i < 16 * chunks; i += 128) {
+            const int r = i / chunks, c = (i - r * chunks) * 8, j = blk * 16 + r;
+            if (j <= last) cp_async16(dst + r * LD + c, base + (size_t)j * W + c);
+            else *reinterpret_cast<uint4*>(dst + r * LD + c) = make_uint4(0, 0, 0, 0);  // rows past the query: never written to the cache yet
+        }
+    };
+    if (b_lo < b_hi) stage(b_lo, 0);
+    __syncthreads();
+    // this warp's query fragments: k-steps warp, warp + 4, ...
+    const int nks = W16 / 16;
+    uint32_t af[KSW][4];
+#pragma unroll
+    for (int i = 0; i < KSW; i++) {
+        const int ks = warp + 4 * i;
+        if (ks < nks) ldsm_x4(af[i], sQ + (lane & 15) * LD + ks * 16 + (lane >> 4) * 8);
+        else af[i][0] = af[i][1] = af[i][2] = af[i][3] = 0;
+    }
+    const int ntw = (rank / 8 + 3) / 4;  // n-tiles per warp
+    const int nt0 = warp * ntw;          // first n-tile of this warp
+    float acc[NTW][4];
+#pragma unroll
+    for (int i = 0; i < NTW; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    float mx0 = -INFINITY, mx1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    for (int blk = b_lo; blk < b_hi; blk++) {
+        const int buf = (blk - b_lo) & 1;
+        cp_async_wait_all();
+        __syncthreads();  // tile `blk` is in place; every warp is done with the other buffer and with sS
+        if (blk + 1 < b_hi) stage(blk + 1, buf ^ 1);
+        const uint16_t* sK = sK0 + buf * 16 * LD;
+        float sp4[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int i = 0; i < KSW; i++) {
+            const int ks = warp + 4 * i;
+            if (ks < nks) {
+                uint32_t b[4];  // (keys 0-7, k lo) (keys 0-7, k hi) (keys 8-15, k lo) (keys 8-15, k hi)
+                ldsm_x4(b, sK + ((lane & 7) + (lane >> 4) * 8) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma16816(sp4[0], af[i], b[0], b[1]);
+                mma16816(sp4[1], af[i], b[2], b[3]);
+            }
+        }
+        float4* sS4 = reinterpret_cast<float4*>(sS);
+        sS4[(warp * 2 + 0) * 32 + lane] = make_float4(sp4[0][0], sp4[0][1], sp4[0][2], sp4[0][3]);
+        sS4[(warp * 2 + 1) * 32 + lane] = make_float4(sp4[1][0], sp4[1][1], sp4[1][2], sp4[1][3]);
+        __syncthreads();
+        float sc[2][4];
+#pragma unroll
+        for (int t = 0; t < 2; t++) {
+            sc[t][0] = sc[t][1] = sc[t][2] = sc[t][3] = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                const float4 v = sS4[(w * 2 + t) * 32 + lane];
+                sc[t][0] += v.x, sc[t][1] += v.y, sc[t][2] += v.z, sc[t][3] += v.w;
+            }
+        }
+        // causal mask: key index of fragment entry (t, e) is blk*16 + t*8 + tg*2 + (e & 1); rows: e < 2 -> gr, else gr + 8
+        const int j0 = blk * 16 + tg * 2;
+#pragma unroll
+        for (int t = 0; t < 2; t++)
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                if (j0 + t * 8 + (e & 1) > last) sc[t][e] = -INFINITY;
+        float r0 = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+        float r1 = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
+        r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, 1)), r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, 2));
+        r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, 1)), r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, 2));
+        const float n0 = fmaxf(mx0, r0), n1 = fmaxf(mx1, r1);  // finite: key blk*16 <= last is never masked
+        const float c0 = expf(mx0 - n0), c1 = expf(mx1 - n1);
+        float p[2][4];
+#pragma unroll
+        for (int t = 0; t < 2; t++) {
+            p[t][0] = expf(sc[t][0] - n0), p[t][1] = expf(sc[t][1] - n0);
+            p[t][2] = expf(sc[t][2] - n1), p[t][3] = expf(sc[t][3] - n1);
+        }
+        float s0 = p[0][0] + p[0][1] + p[1][0] + p[1][1], s1 = p[0][2] + p[0][3] + p[1][2] + p[1][3];
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 1), s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 1), s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+        l0 = l0 * c0 + s0, l1 = l1 * c1 + s1, mx0 = n0, mx1 = n1;
+        // P as A fragments, hi and lo parts: a0 (gr, k 0-7) a1 (gr+8, k 0-7) a2 (gr, k 8-15) a3 (gr+8, k 8-15)
+        uint32_t ph[4], pl[4];
+        auto split = [&](float a, float b, uint32_t& hi, uint32_t& lo) {
+            const __nv_bfloat16 ah = __float2bfloat16_rn(a), bh = __float2bfloat16_rn(b);
+            hi = pack_bf16x2(__bfloat162float(ah), __bfloat162float(bh));
+            lo = pack_bf16x2(a - __bfloat162float(ah), b - __bfloat162float(bh));
+        };
+        split(p[0][0], p[0][1], ph[0], pl[0]);
+        split(p[0][2], p[0][3], ph[1], pl[1]);
+        split(p[1][0], p[1][1], ph[2], pl[2]);
+        split(p[1][2], p[1][3], ph[3], pl[3]);
+#pragma unroll
+        for (int i = 0; i < NTW; i += 2) {
+            if (i < ntw) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) acc[i][e] *= (e < 2 ? c0 : c1), acc[i + 1][e] *= (e < 2 ? c0 : c1);
+                const int nt = nt0 + i;  // two n-tiles per ldmatrix: (keys 0-7, n) (keys 8-15, n) (keys 0-7, n + 8) (keys 8-15, n + 8)
+                if (nt * 8 < rank) {
+                    uint32_t b[4];
+                    int col = nt * 8 + (lane >> 4) * 8;
+                    if (col >= W16) col = nt * 8;  // the second tile lies past the row: fetch the first again, its result is dropped
+                    ldsm_x4_t(b, sK + (lane & 15) * LD + col);
+                    mma16816(acc[i], ph, b[0], b[1]);
+                    mma16816(acc[i], pl, b[0], b[1]);
+                    if (i + 1 < ntw && (nt + 1) * 8 < rank) {
+                        mma16816(acc[i + 1], ph, b[2], b[3]);
+                        mma16816(acc[i + 1], pl, b[2], b[3]);
+                    }
+                }
+            }
+        }
+    }
+    // partial results of this split: rows gr and gr + 8 of the head group
+    const int h0 = hg * 16 + gr, h1 = h0 + 8;
+    float* po0 = part_o + (((size_t)m * HG * 16 + h0) * S + sp) * rank;
+    float* po1 = part_o + (((size_t)m * HG * 16 + h1) * S + sp) * rank;
+#pragma unroll
+    for (int i = 0; i < NTW; i++) {
+        const int c = (nt0 + i) * 8 + tg * 2;
+        if (i < ntw && c < rank) {
+            *reinterpret_cast<float2*>(po0 + c) = make_float2(acc[i][0], acc[i][1]);
+            *reinterpret_cast<float2*>(po1 + c) = make_float2(acc[i][2], acc[i][3]);
+        }
+    }
+    if (warp == 0 && tg == 0) {
+        float* ml0 = part_ml + (((size_t)m * HG * 16 + h0) * S + sp) * 2;
+        float* ml1 = part_ml + (((size_t)m * HG * 16 + h1) * S + sp) * 2;
+        ml0[0] = mx0, ml0[1] = l0, ml1[0] = mx1, ml1[1] = l1;
+    }
+}
+// out[m][h] = sum_s O_s exp(m_s - M) / (exp(sink_h - M) + sum_s l_s exp(m_s - M)),  M = max(sink_h, m_s)
+__global__ void __launch_bounds__(128) kf_latent_merge_kernel(float* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                              const uint16_t* __restrict__ sink, int H, int HG, int rank, int S) {
+    const int m = blockIdx.x, h = blockIdx.y;
+    const float* ml = part_ml + ((size_t)m * HG * 16 + h) * S * 2;
+    const float* po = part_o + ((size_t)m * HG * 16 + h) * S * rank;
+    const float sk = bf16_bits_to_f32(sink[h]);
+    float M = sk;
+    for (int s = 0; s < S; s++) M = fmaxf(M, ml[2 * s]);
+    float den = expf(sk - M);
+    for (int s = 0; s < S; s++) den += ml[2 * s] == -INFINITY ? 0.f : ml[2 * s + 1] * expf(ml[2 * s] - M);
+    float* o = out + ((size_t)m * H + h) * rank;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < S; s++)
+            if (ml[2 * s] != -INFINITY) v = fmaf(po[(size_t)s * rank + c], expf(ml[2 * s] - M), v);
+        o[c] = v / den;
+    }
+}
 // head outputs: o[m][h*dv + e] = (W_uv[h*dv + e] . lat[m][h]) * sigmoid(gate[m][h*dv + e]) in the activation type; warp per output
 template <typename TO>
 __global__ void __launch_bounds__(256) kf_latent_expand_kernel(TO* __restrict__ o, const float* __restrict__ lat, const uint16_t* __restrict__ Wuv,
@@ -296,11 +498,11 @@ extern "C" int kf_conv_silu(kf_ctx* ctx, float* xbc_out, const float* u, int ldu
                             size_t tail_stride, const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int C, int K) {
     if (!ctx || !xbc_out || !u || !w_bf16 || !tail || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, nseq >= 1 && T >= 1 && C >= 1 && K >= 1 && tail_stride >= (size_t)(K - 1) * C, "shape");
-    kf_conv_silu_kernel<<<nseq * T, 256, 0, ctx->stream>>>(xbc_out, u + c0, ldu, (const uint16_t*)w_bf16, (const uint16_t*)b_bf16, tail, tail_stride, pos_dev,
+    kf_conv_silu_kernel<<<dim3(nseq * T, (C + 255) / 256), 256, 0, ctx->stream>>>(xbc_out, u + c0, ldu, (const uint16_t*)w_bf16, (const uint16_t*)b_bf16, tail, tail_stride, pos_dev,
                                                            slot_dev, T, C, K);
     KF_LAUNCH_CHECK(ctx);
     if (K > 1) {
-        kf_conv_tail_kernel<<<nseq, 256, 0, ctx->stream>>>(tail, tail_stride, u + c0, ldu, pos_dev, slot_dev, T, C, K);
+        kf_conv_tail_kernel<<<dim3(nseq, (C + 255) / 256), 256, 0, ctx->stream>>>(tail, tail_stride, u + c0, ldu, pos_dev, slot_dev, T, C, K);
         KF_LAUNCH_CHECK(ctx);
     }
     return KF_OK;
@@ -345,13 +547,38 @@ extern "C" int kf_latent_append(kf_ctx* ctx, void* cache, int cache_f32, size_t 
 // [dn plain | rot_dim rotated]; w_uk bf16 [H*dn][rank]; sink bf16 [H]; qa_work: float scratch [M][H][rank + rot_dim].
 extern "C" int kf_latent_attention(kf_ctx* ctx, float* lat_out, float* qa_work, const float* q, int ldq, const void* w_uk_bf16, const void* sink_bf16,
                                    const void* cache, int cache_f32, size_t slot_stride, const float* inv_freq_dev, const int32_t* pos_dev,
-                                   const int32_t* slot_dev, int M, int H, int dn, int rot_dim, int rot_dims, int rank, float scale) {
+                                   const int32_t* slot_dev, int M, int H, int dn, int rot_dim, int rot_dims, int rank, float scale, int max_pos_hint) {
     if (!ctx || !lat_out || !qa_work || !q || !w_uk_bf16 || !sink_bf16 || !cache || !inv_freq_dev || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, M >= 1 && H >= 1 && dn >= 1 && rank >= 1 && rank + rot_dim <= 32 * LMAX && rot_dims <= rot_dim && rot_dims % 2 == 0, "rank + rot_dim <= 640");
     dim3 grid(M, H), qgrid((M + QT - 1) / QT, H);
     kf_latent_query_kernel<<<qgrid, 128, (size_t)QT * (dn + rot_dim) * 4, ctx->stream>>>(qa_work, q, ldq, (const uint16_t*)w_uk_bf16, inv_freq_dev, pos_dev, M,
                                                                                        H, dn, rot_dim, rot_dims, rank, scale);
     KF_LAUNCH_CHECK(ctx);
+    if (!cache_f32 && rank % 8 == 0 && (rank + rot_dim) % 8 == 0 && rank <= NTW * 32 && rank + rot_dim <= KSW * 64 && (slot_stride * 2) % 16 == 0 &&
+        ((uintptr_t)cache & 15) == 0) {
+        // tensor-core path: 16 heads per CTA; keys split over CTAs when tokens x head groups alone would leave SMs idle
+        const int HG = (H + 15) / 16, W16 = (rank + rot_dim + 15) & ~15, LD = W16 + 8;
+        const int nblk = (std::max(0, max_pos_hint) + 16) / 16;
+        int S = std::max(1, std::min((2 * ctx->sm_count) / std::max(1, M * HG), (nblk + 3) / 4));
+        S = std::min(S, 64);
+        const size_t rows = (size_t)M * HG * 16 * S;
+        KF_REQUIRE(ctx, kf_ensure_attn_ws(ctx, rows * (rank + 2) * sizeof(float)) == KF_OK, "attention workspace");
+        float* part_o  = ctx->attn_ws;
+        float* part_ml = part_o + rows * rank;
+        const size_t smem = (size_t)3 * 16 * LD * 2 + 4 * 2 * 32 * 16;
+        static bool attr_set = false;
+        if (!attr_set) {
+            KF_CUDA(ctx, cudaFuncSetAttribute(kf_latent_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+            attr_set = true;
+        }
+        KF_REQUIRE(ctx, smem <= 96 * 1024, "row too wide for the staging area");
+        kf_latent_attn_mma_kernel<<<dim3(M, HG, S), 128, smem, ctx->stream>>>(part_o, part_ml, qa_work, (const uint16_t*)cache, slot_stride, pos_dev, slot_dev,
+                                                                             H, HG, rank, rot_dim, S);
+        KF_LAUNCH_CHECK(ctx);
+        kf_latent_merge_kernel<<<grid, 128, 0, ctx->stream>>>(lat_out, part_o, part_ml, (const uint16_t*)sink_bf16, H, HG, rank, S);
+        KF_LAUNCH_CHECK(ctx);
+        return KF_OK;
+    }
     const size_t smem = (size_t)(4 * rank + 8) * 4;
     if (cache_f32)
         kf_latent_attn_kernel<float><<<grid, 128, smem, ctx->stream>>>(lat_out, qa_work, (const float*)cache, slot_stride, (const uint16_t*)sink_bf16, pos_dev,

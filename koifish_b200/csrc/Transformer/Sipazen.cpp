@@ -318,7 +318,7 @@ int LatentAttention::cuInfer(int M) {
     KF_TRY(kf_latent_append(f.ctx, sl.rows, ak, sl.row_stride, s.v, W, dkv_norm->data, inv_freq, f.d_pos, f.d_slot, M, m.kv_rank, m.rot_dim, m.rot_dims,
                             f.config.norm_rms_eps));
     KF_TRY(kf_latent_attention(f.ctx, s.lat, s.y, s.u, q->ne[0], uk->data, sink->data, sl.rows, ak, sl.row_stride, inv_freq, f.d_pos, f.d_slot, M, m.heads,
-                               m.dim, m.rot_dim, m.rot_dims, m.kv_rank, m.scale));
+                               m.dim, m.rot_dim, m.rot_dims, m.kv_rank, m.scale, f.attn_hint));
     KF_TRY(kf_latent_expand(f.ctx, s.act, ak, s.lat, uv->data, s.g, m.heads * m.vdim, M, m.heads, m.vdim, m.kv_rank));
     KF_TRY(Lin(f, s.sub, o, s.act, M));
     return KF_OK;
