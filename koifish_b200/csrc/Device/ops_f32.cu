@@ -97,6 +97,64 @@ __global__ void __launch_bounds__(128) kf_moe_route_kernel(int32_t* __restrict__
         for (int j = lane; j < top; j += 32) wgt[(size_t)m * top + j] /= den;
     }
 }
+// few tokens (decode): routing and the dispatch tables in ONE block -- warps route the tokens, then thread i ranks entry i among the
+// earlier entries of its expert, thread e counts expert e, thread 0 scans the counts
+constexpr int kRouteSmall = 256;
+__global__ void __launch_bounds__(256) kf_moe_route_small_kernel(int32_t* __restrict__ idx, float* __restrict__ wgt, int32_t* __restrict__ offsets,
+                                                                 int32_t* __restrict__ entry_slot, int32_t* __restrict__ slot_row,
+                                                                 int32_t* __restrict__ slot_group, const float* __restrict__ logits, int ldl,
+                                                                 const uint16_t* __restrict__ bias, int M, int E, int top) {
+    __shared__ int sidx[kRouteSmall];
+    __shared__ int srank[kRouteSmall];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = M * top;
+    for (int m = warp; m < M; m += 8) {
+        const float* lg = logits + (size_t)m * ldl;
+        float first = 0.f, den = 0.f;
+        for (int j = 0; j < top; j++) {
+            float best = -INFINITY;
+            int bi     = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                bool taken = false;
+                for (int q = 0; q < j; q++) taken = taken || sidx[m * top + q] == e;
+                if (taken) continue;
+                const float v = lg[e] + (bias ? bf16_bits_to_f32(bias[e]) : 0.f);
+                if (v > best || (v == best && e < bi)) best = v, bi = e;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi   = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ob > best || (ob == best && oi < bi)) best = ob, bi = oi;
+            }
+            if (j == 0) first = best;
+            const float p = expf(best - first);
+            den += p;
+            if (lane == 0) sidx[m * top + j] = bi, idx[(size_t)m * top + j] = bi, wgt[(size_t)m * top + j] = p;
+            __syncwarp();
+        }
+        for (int j = lane; j < top; j += 32) wgt[(size_t)m * top + j] /= den;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        int r = 0;
+        for (int j = 0; j < i; j++) r += sidx[j] == sidx[i];
+        srank[i] = r;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {  // offsets by a running count over the entries' experts: E may be large, n is small
+        int s = 0;
+        for (int e = 0; e < E; e++) {
+            offsets[e] = s;
+            for (int j = 0; j < n; j++) s += sidx[j] == e;
+        }
+        offsets[E] = s;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int e = sidx[i], sl = offsets[e] + srank[i];
+        entry_slot[i] = sl, slot_row[sl] = i / top, slot_group[sl] = e;
+    }
+}
 // one block per expert: the entries (token, choice) routed to it, ranked in entry order (ballot + popc compaction)
 __global__ void __launch_bounds__(256) kf_moe_rank_kernel(int32_t* __restrict__ rank, int32_t* __restrict__ count, const int32_t* __restrict__ idx, int n) {
     __shared__ int wsum[8];
@@ -205,6 +263,11 @@ extern "C" int kf_moe_route(kf_ctx* ctx, int32_t* idx, float* wgt, int32_t* offs
     if (!ctx || !idx || !wgt || !offsets || !entry_slot || !slot_row || !slot_group || !work || !logits) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, M >= 1 && E >= 1 && top >= 1 && top <= E && ldl >= E, "1 <= top <= experts");
     const int n = M * top;
+    if (n <= kRouteSmall && (long long)E * n <= 16384) {
+        kf_moe_route_small_kernel<<<1, 256, 0, ctx->stream>>>(idx, wgt, offsets, entry_slot, slot_row, slot_group, logits, ldl, (const uint16_t*)bias_bf16, M, E, top);
+        KF_LAUNCH_CHECK(ctx);
+        return KF_OK;
+    }
     int32_t *rank = work, *count = work + n;
     kf_moe_route_kernel<<<(M + 3) / 4, 128, 0, ctx->stream>>>(idx, wgt, logits, ldl, (const uint16_t*)bias_bf16, M, E, top);
     KF_LAUNCH_CHECK(ctx);

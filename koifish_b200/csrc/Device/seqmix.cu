@@ -86,6 +86,7 @@ __global__ void __launch_bounds__(1024) kf_ssm_scan_kernel(float* __restrict__ y
         const int n = r * NPT + i;
         S[i] = (live && n < N && !fresh) ? st[n] : 0.f;
     }
+    const bool vec4 = (N & 3) == 0;
     const float Aneg = -expf(bf16_bits_to_f32(A_log[h])), Dh = bf16_bits_to_f32(Dw[h]), dtb = bf16_bits_to_f32(dt_bias[h]);
     for (int t0 = 0; t0 < T; t0 += TB) {
         const int nt = min(TB, T - t0);
@@ -109,12 +110,25 @@ __global__ void __launch_bounds__(1024) kf_ssm_scan_kernel(float* __restrict__ y
             const float dtv = sDt[tt], av = sA[tt], xv = sX[tt * PB + (pl < PB ? pl : 0)];
             const float dx = dtv * xv;
             float acc = 0.f;
+            if (vec4 && (r + 1) * NPT <= N) {  // this thread's 16 rows as four 16-byte loads each of B and C
+                const float4* b4 = reinterpret_cast<const float4*>(sB + tt * N + r * NPT);
+                const float4* c4 = reinterpret_cast<const float4*>(sC + tt * N + r * NPT);
 #pragma unroll
-            for (int i = 0; i < NPT; i++) {
-                const int n = r * NPT + i;
-                if (n < N) {
-                    S[i] = fmaf(av, S[i], dx * sB[tt * N + n]);
-                    acc  = fmaf(S[i], sC[tt * N + n], acc);
+                for (int i = 0; i < NPT / 4; i++) {
+                    const float4 bv = b4[i], cv = c4[i];
+                    S[4 * i + 0] = fmaf(av, S[4 * i + 0], dx * bv.x), acc = fmaf(S[4 * i + 0], cv.x, acc);
+                    S[4 * i + 1] = fmaf(av, S[4 * i + 1], dx * bv.y), acc = fmaf(S[4 * i + 1], cv.y, acc);
+                    S[4 * i + 2] = fmaf(av, S[4 * i + 2], dx * bv.z), acc = fmaf(S[4 * i + 2], cv.z, acc);
+                    S[4 * i + 3] = fmaf(av, S[4 * i + 3], dx * bv.w), acc = fmaf(S[4 * i + 3], cv.w, acc);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < NPT; i++) {
+                    const int n = r * NPT + i;
+                    if (n < N) {
+                        S[i] = fmaf(av, S[i], dx * sB[tt * N + n]);
+                        acc  = fmaf(S[i], sC[tt * N + n], acc);
+                    }
                 }
             }
             for (int o = R >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -181,7 +195,7 @@ __global__ void __launch_bounds__(128) kf_latent_query_kernel(float* __restrict_
         sq[t * D + d] = q[(size_t)(m0 + t) * ldq + (size_t)h * D + d];
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+    for (int c = blockIdx.z * blockDim.x + threadIdx.x; c < rank; c += gridDim.z * blockDim.x) {
         float s[QT];
 #pragma unroll
         for (int t = 0; t < QT; t++) s[t] = 0.f;
@@ -195,7 +209,7 @@ __global__ void __launch_bounds__(128) kf_latent_query_kernel(float* __restrict_
             if (t < nt) qa[((size_t)(m0 + t) * H + h) * W + c] = s[t] * scale;
     }
     const int half = dims / 2;
-    for (int i = threadIdx.x; i < nt * rot_dim; i += blockDim.x) {
+    for (int i = blockIdx.z * blockDim.x + threadIdx.x; i < nt * rot_dim; i += gridDim.z * blockDim.x) {
         const int t = i / rot_dim, e = i - t * rot_dim;
         const float* sr = sq + t * D + dn;
         float v = sr[e];
@@ -517,7 +531,8 @@ extern "C" int kf_ssm_scan(kf_ctx* ctx, float* y, int ldy, const float* xbc, con
     KF_REQUIRE(ctx, state_stride >= (size_t)H * P * N, "state stride");
     int R = 1;
     while (R * NPT < N) R <<= 1;
-    const int PB = std::min(P, 1024 / R);
+    int PB = std::min(P, 1024 / R);
+    while (PB > 16 && (long long)H * nseq * ((P + PB - 1) / PB) < ctx->sm_count) PB = (PB + 1) / 2;  // fewer heads than SMs: split the columns
     const int threads = ((PB * R + 31) / 32) * 32;
     const size_t smem = (size_t)(2 * TB * N + TB * PB + 2 * TB) * sizeof(float);
     KF_REQUIRE(ctx, smem <= 48 * 1024, "state too large for the staging area");
@@ -550,7 +565,7 @@ extern "C" int kf_latent_attention(kf_ctx* ctx, float* lat_out, float* qa_work, 
                                    const int32_t* slot_dev, int M, int H, int dn, int rot_dim, int rot_dims, int rank, float scale, int max_pos_hint) {
     if (!ctx || !lat_out || !qa_work || !q || !w_uk_bf16 || !sink_bf16 || !cache || !inv_freq_dev || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, M >= 1 && H >= 1 && dn >= 1 && rank >= 1 && rank + rot_dim <= 32 * LMAX && rot_dims <= rot_dim && rot_dims % 2 == 0, "rank + rot_dim <= 640");
-    dim3 grid(M, H), qgrid((M + QT - 1) / QT, H);
+    dim3 grid(M, H), qgrid((M + QT - 1) / QT, H, (rank + 127) / 128);
     kf_latent_query_kernel<<<qgrid, 128, (size_t)QT * (dn + rot_dim) * 4, ctx->stream>>>(qa_work, q, ldq, (const uint16_t*)w_uk_bf16, inv_freq_dev, pos_dev, M,
                                                                                        H, dn, rot_dim, rot_dims, rank, scale);
     KF_LAUNCH_CHECK(ctx);

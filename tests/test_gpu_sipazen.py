@@ -239,6 +239,17 @@ def test_stack_prompt_and_decode(ctx, f32):
     m.close()
 
 
+@pytest.mark.parametrize("f32", [True, False])
+def test_wide_panels(ctx, f32):
+    """panels of up to 192 tokens: the matmuls take their tile kernels, the router its many-token dispatch (one block per expert)"""
+    cfg = config(FULL)
+    W = weights(cfg, seed=13)
+    toks = tokens(230, cfg["vocab"], 12)
+    m = build(ctx, cfg, W, f32, panel=192)
+    assert close(run_cut(m, toks, [192, 17, 2]), oracle(cfg, W, toks), f32)
+    m.close()
+
+
 def test_portions_of_many_sizes(ctx):
     cfg = config(FULL)
     W = weights(cfg, seed=6)
