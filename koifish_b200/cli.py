@@ -106,7 +106,7 @@ def main(argv=None):
     t.add_argument("--out", required=True)
     t.add_argument("--max-tokens", type=int, default=4096)
     t.add_argument("--panel", type=int, default=512, help="tokens per forward panel")
-    t.add_argument("--slots", type=int, default=2, help="sequence slots of the cache / state manager")
+    t.add_argument("--slots", type=int, default=4, help="sequence slots of the cache / state manager")
     t.set_defaults(fn=cmd_trace)
     args = ap.parse_args(argv)
     return args.fn(args)

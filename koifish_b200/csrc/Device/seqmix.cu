@@ -81,9 +81,12 @@ __global__ void __launch_bounds__(1024) kf_ssm_scan_kernel(float* __restrict__ y
     float* st = state + (size_t)slot[m0] * state_stride + ((size_t)h * P + (live ? p : 0)) * N;
     float S[NPT];
     const bool fresh = pos[m0] == 0;
+    // state row held in S[i]: the rows are dealt to the R lanes of a column four at a time, n = ((i / 4) * R + r) * 4 + i % 4, so that the
+    // lanes' 16-byte loads of B and C are consecutive in shared memory
+#define KF_SSM_ROW(i) ((((i) >> 2) * R + r) * 4 + ((i) & 3))
 #pragma unroll
     for (int i = 0; i < NPT; i++) {
-        const int n = r * NPT + i;
+        const int n = KF_SSM_ROW(i);
         S[i] = (live && n < N && !fresh) ? st[n] : 0.f;
     }
     const bool vec4 = (N & 3) == 0;
@@ -110,12 +113,14 @@ __global__ void __launch_bounds__(1024) kf_ssm_scan_kernel(float* __restrict__ y
             const float dtv = sDt[tt], av = sA[tt], xv = sX[tt * PB + (pl < PB ? pl : 0)];
             const float dx = dtv * xv;
             float acc = 0.f;
-            if (vec4 && (r + 1) * NPT <= N) {  // this thread's 16 rows as four 16-byte loads each of B and C
-                const float4* b4 = reinterpret_cast<const float4*>(sB + tt * N + r * NPT);
-                const float4* c4 = reinterpret_cast<const float4*>(sC + tt * N + r * NPT);
+            if (vec4) {  // this thread's 16 rows as four 16-byte loads each of B and C
+                const float4* b4 = reinterpret_cast<const float4*>(sB + tt * N);
+                const float4* c4 = reinterpret_cast<const float4*>(sC + tt * N);
 #pragma unroll
                 for (int i = 0; i < NPT / 4; i++) {
-                    const float4 bv = b4[i], cv = c4[i];
+                    const int q = i * R + r;
+                    if (q * 4 >= N) continue;
+                    const float4 bv = b4[q], cv = c4[q];
                     S[4 * i + 0] = fmaf(av, S[4 * i + 0], dx * bv.x), acc = fmaf(S[4 * i + 0], cv.x, acc);
                     S[4 * i + 1] = fmaf(av, S[4 * i + 1], dx * bv.y), acc = fmaf(S[4 * i + 1], cv.y, acc);
                     S[4 * i + 2] = fmaf(av, S[4 * i + 2], dx * bv.z), acc = fmaf(S[4 * i + 2], cv.z, acc);
@@ -124,7 +129,7 @@ __global__ void __launch_bounds__(1024) kf_ssm_scan_kernel(float* __restrict__ y
             } else {
 #pragma unroll
                 for (int i = 0; i < NPT; i++) {
-                    const int n = r * NPT + i;
+                    const int n = KF_SSM_ROW(i);
                     if (n < N) {
                         S[i] = fmaf(av, S[i], dx * sB[tt * N + n]);
                         acc  = fmaf(S[i], sC[tt * N + n], acc);
@@ -138,10 +143,11 @@ __global__ void __launch_bounds__(1024) kf_ssm_scan_kernel(float* __restrict__ y
     if (live) {
 #pragma unroll
         for (int i = 0; i < NPT; i++) {
-            const int n = r * NPT + i;
+            const int n = KF_SSM_ROW(i);
             if (n < N) st[n] = S[i];
         }
     }
+#undef KF_SSM_ROW
 }
 
 // ------------------------------------------------------------------------------------------------------------ latent attention

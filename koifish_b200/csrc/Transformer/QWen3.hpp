@@ -27,7 +27,8 @@ struct MIXER_CARD {
     // latent attention: per head `dim` plain + `rot_dim` rotated query/key entries, values of vdim, latent rank; rotation on the first
     // rot_dims entries of the rotated part with frequencies rot_base^(-2i/rot_dims); score scale
     int dim = 0, rot_dim = 0, kv_rank = 0, rot_dims = 0;
-    float rot_base = 10000.f, scale = 1.f;
+    double rot_base = 10000.0;
+    float scale = 1.f;
 };
 struct MOE_CARD {
     bool present = false;

@@ -27,10 +27,10 @@ static int need_int(const JSON& j, const char* key, const std::string& where) {
 static void ParseSipazen(const JSON& h, MODEL_CARD& c) {
     c.vocab         = need_int(h, "vocab", "config");
     c.n_embd        = need_int(h, "width", "config");
-    c.residual_mult = (float)h.at("residual_mult").as_double(1.0);
+    if (const JSON* r = h.find("residual_mult")) c.residual_mult = (float)r->as_double(1.0);
     const JSON& nm  = h.at("norm");
     c.norm_rms_eps  = (float)nm.at("eps").as_double(1e-5);
-    c.norm_groups   = need_int(nm, "groups", "norm");
+    c.norm_groups   = nm.contains("groups") ? need_int(nm, "groups", "norm") : 1;
     const JSON& ls  = h.at("layers");
     if (!ls.is_array() || ls.arr.empty()) throw std::runtime_error("config: layers must be a non-empty list");
     for (size_t i = 0; i < ls.arr.size(); i++) {
@@ -42,16 +42,21 @@ static void ParseSipazen(const JSON& h, MODEL_CARD& c) {
         const JSON& x = l.at("mixer");
         if (m.type == "mamba2") {
             m.heads = need_int(x, "heads", where), m.vdim = need_int(x, "vdim", where), m.state = need_int(x, "state", where);
-            m.groups = need_int(x, "groups", where), m.norm_groups = need_int(x, "norm_groups", where), m.conv = need_int(x, "conv", where);
+            m.groups = x.contains("groups") ? need_int(x, "groups", where) : 1;
+            m.norm_groups = x.contains("norm_groups") ? need_int(x, "norm_groups", where) : 1;
+            m.conv = need_int(x, "conv", where);
             if (m.heads < 1 || m.vdim < 1 || m.state < 1 || m.groups < 1 || m.heads % m.groups || m.conv < 1 || m.norm_groups < 1 ||
                 (m.heads * m.vdim) % m.norm_groups)
                 throw std::runtime_error("config: " + where + ": groups must divide heads, norm_groups must divide heads * vdim");
         } else if (m.type == "latent_attention") {
             m.heads = need_int(x, "heads", where), m.dim = need_int(x, "dim", where), m.rot_dim = need_int(x, "rot_dim", where);
             m.vdim = need_int(x, "vdim", where), m.kv_rank = need_int(x, "kv_rank", where);
-            m.scale = (float)x.at("scale").as_double(1.0);
-            const JSON& r = x.at("rot");
-            m.rot_base = (float)r.at("base").as_double(10000.0), m.rot_dims = need_int(r, "dims", where + ".rot");
+            m.scale = x.contains("scale") ? (float)x.at("scale").as_double(1.0) : 1.0f / std::sqrt((float)(m.dim + m.rot_dim));
+            m.rot_dims = m.rot_dim;
+            if (const JSON* r = x.find("rot")) {
+                if (r->contains("base")) m.rot_base = r->at("base").as_double(10000.0);
+                if (r->contains("dims")) m.rot_dims = need_int(*r, "dims", where + ".rot");
+            }
             if (m.heads < 1 || m.dim < 1 || m.rot_dim < 0 || m.vdim < 1 || m.kv_rank < 1 || m.rot_dims < 0 || m.rot_dims > m.rot_dim || m.rot_dims % 2)
                 throw std::runtime_error("config: " + where + ": rot.dims must be even and at most rot_dim");
         } else {
@@ -178,7 +183,7 @@ static int BuildSipazen(Fish& f) {
             b.Tensor(p + "mix.o", E, m.heads * m.vdim, a->o);
             // rotation frequencies base^(-2i/dims), evaluated in double and rounded once
             std::vector<float> fr((size_t)std::max(1, m.rot_dims / 2));
-            for (int k = 0; k < m.rot_dims / 2; k++) fr[k] = (float)std::pow((double)m.rot_base, -2.0 * k / (double)m.rot_dims);
+            for (int k = 0; k < m.rot_dims / 2; k++) fr[k] = (float)std::pow(m.rot_base, -2.0 * k / (double)m.rot_dims);
             KF_TRY(b.Buf(&a->inv_freq, fr.size() * 4));
             KF_TRY(kf_h2d(f.ctx, a->inv_freq, fr.data(), fr.size() * 4));
             KF_TRY(kf_ctx_sync(f.ctx));
