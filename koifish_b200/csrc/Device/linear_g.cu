@@ -104,6 +104,10 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, cons
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
 // 8 consecutive k of one row: thread t fetches row t / 4, k offset (t % 4) * 8
 template <typename T>
 struct __align__(16) Frag8 {
@@ -166,8 +170,12 @@ __global__ void __launch_bounds__(256) kf_lin_tile_kernel(LinArgs a) {
     if (DUAL) fetch8<uint16_t>(fw1, W1, woff, lk, a.K, wok, wvec);
     for (int k0 = 0; k0 < a.K; k0 += BK) {
         __syncthreads();  // the previous step's fragments have been read
-#pragma unroll
-        for (int j = 0; j < 8; j++) sx[lr][lk + j] = fx.v[j];
+        if (MMA) {
+            *reinterpret_cast<uint4*>(&sx[lr][lk]) = *reinterpret_cast<const uint4*>(fx.v);
+        } else {
+            *reinterpret_cast<float4*>(&sx[lr][lk])     = *reinterpret_cast<const float4*>(fx.v);
+            *reinterpret_cast<float4*>(&sx[lr][lk + 4]) = *reinterpret_cast<const float4*>(fx.v + 4);
+        }
         *reinterpret_cast<uint4*>(&sw0[lr][lk]) = *reinterpret_cast<const uint4*>(fw0.v);
         if (DUAL) *reinterpret_cast<uint4*>(&sw1[lr][lk]) = *reinterpret_cast<const uint4*>(fw1.v);
         __syncthreads();
@@ -177,26 +185,23 @@ __global__ void __launch_bounds__(256) kf_lin_tile_kernel(LinArgs a) {
             if (DUAL) fetch8<uint16_t>(fw1, W1, woff, k0 + BK + lk, a.K, wok, wvec);
         }
         if (MMA) {
-            const int gr = lane >> 2, tg = lane & 3;
+            // fragments through ldmatrix: A = 16 rows x 16 k of this warp's slots; B = two 8-output tiles per instruction
             const uint16_t* xa = (const uint16_t*)&sx[wm * 16][0];
 #pragma unroll
             for (int kk = 0; kk < BK; kk += 16) {
                 uint32_t af[4];
-                af[0] = *reinterpret_cast<const uint32_t*>(xa + (gr)*LDS + kk + tg * 2);
-                af[1] = *reinterpret_cast<const uint32_t*>(xa + (gr + 8) * LDS + kk + tg * 2);
-                af[2] = *reinterpret_cast<const uint32_t*>(xa + (gr)*LDS + kk + tg * 2 + 8);
-                af[3] = *reinterpret_cast<const uint32_t*>(xa + (gr + 8) * LDS + kk + tg * 2 + 8);
+                ldsm_x4(af, xa + (lane & 15) * LDS + kk + (lane >> 4) * 8);
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const int nr = wn * 32 + j * 8 + gr;
-                    uint32_t bf[2];
-                    bf[0] = *reinterpret_cast<const uint32_t*>(&sw0[nr][kk + tg * 2]);
-                    bf[1] = *reinterpret_cast<const uint32_t*>(&sw0[nr][kk + tg * 2 + 8]);
+                for (int j = 0; j < 4; j += 2) {
+                    const int nr = wn * 32 + j * 8 + (lane & 7) + (lane >> 4) * 8, kc = kk + ((lane >> 3) & 1) * 8;
+                    uint32_t bf[4];
+                    ldsm_x4(bf, &sw0[nr][kc]);
                     mma_bf16_16816(&acc0[j * 4], af, bf);
+                    mma_bf16_16816(&acc0[(j + 1) * 4], af, bf + 2);
                     if (DUAL) {
-                        bf[0] = *reinterpret_cast<const uint32_t*>(&sw1[nr][kk + tg * 2]);
-                        bf[1] = *reinterpret_cast<const uint32_t*>(&sw1[nr][kk + tg * 2 + 8]);
+                        ldsm_x4(bf, &sw1[nr][kc]);
                         mma_bf16_16816(&acc1[j * 4], af, bf);
+                        mma_bf16_16816(&acc1[(j + 1) * 4], af, bf + 2);
                     }
                 }
             }

@@ -61,12 +61,12 @@ __global__ void kf_conv_tail_kernel(float* __restrict__ tail, size_t tail_stride
 // ------------------------------------------------------------------------------------------------------------ selective scan
 // grid (heads, sequences, p-chunks).  Thread (p, r) keeps NPT consecutive state rows n of column p in registers; the R threads of a
 // column are adjacent lanes and reduce y with shuffles.  Tokens are staged through shared memory TB at a time.
-constexpr int NPT = 16, TB = 16;
+constexpr int NPT = 16;
 __global__ void __launch_bounds__(1024) kf_ssm_scan_kernel(float* __restrict__ y, int ldy, const float* __restrict__ xbc, int C, const float* __restrict__ u,
                                                            int ldu, int z_unused, int dt_off, const uint16_t* __restrict__ dt_bias,
                                                            const uint16_t* __restrict__ A_log, const uint16_t* __restrict__ Dw, float* __restrict__ state,
                                                            size_t state_stride, const int32_t* __restrict__ pos, const int32_t* __restrict__ slot, int T,
-                                                           int H, int P, int N, int G, int R, int PB) {
+                                                           int H, int P, int N, int G, int R, int PB, int TB) {
     extern __shared__ float sm[];
     float* sB  = sm;                 // [TB][N]
     float* sC  = sB + TB * N;        // [TB][N]
@@ -104,9 +104,9 @@ __global__ void __launch_bounds__(1024) kf_ssm_scan_kernel(float* __restrict__ y
             const int tt = i / PB, q = i - tt * PB;
             sX[tt * PB + q] = (p0 + q < P) ? xbc[(size_t)(m0 + t0 + tt) * C + h * P + p0 + q] : 0.f;
         }
-        if (tid < nt) {
-            const float dtv = softplus_f(u[(size_t)(m0 + t0 + tid) * ldu + dt_off + h] + dtb);
-            sDt[tid] = dtv, sA[tid] = expf(Aneg * dtv);
+        for (int i = tid; i < nt; i += blockDim.x) {
+            const float dtv = softplus_f(u[(size_t)(m0 + t0 + i) * ldu + dt_off + h] + dtb);
+            sDt[i] = dtv, sA[i] = expf(Aneg * dtv);
         }
         __syncthreads();
         for (int tt = 0; tt < nt; tt++) {
@@ -540,12 +540,15 @@ extern "C" int kf_ssm_scan(kf_ctx* ctx, float* y, int ldy, const float* xbc, con
     int PB = std::min(P, 1024 / R);
     while (PB > 16 && (long long)H * nseq * ((P + PB - 1) / PB) < ctx->sm_count) PB = (PB + 1) / 2;  // fewer heads than SMs: split the columns
     const int threads = ((PB * R + 31) / 32) * 32;
+    // tokens staged per pass: as many as fit 40 KB (each pass exposes one global-memory round trip), at most 64
+    int TB = (int)std::min<size_t>(64, (40 * 1024 / sizeof(float)) / (size_t)(2 * N + PB + 2));
+    TB = std::max(4, std::min(TB, T));
     const size_t smem = (size_t)(2 * TB * N + TB * PB + 2 * TB) * sizeof(float);
     KF_REQUIRE(ctx, smem <= 48 * 1024, "state too large for the staging area");
     dim3 grid(H, nseq, (P + PB - 1) / PB);
     kf_ssm_scan_kernel<<<grid, threads, smem, ctx->stream>>>(y, ldy, xbc, H * P + 2 * G * N, u, ldu, 0, dt_off, (const uint16_t*)dt_bias_bf16,
                                                             (const uint16_t*)A_log_bf16, (const uint16_t*)D_bf16, state, state_stride, pos_dev, slot_dev, T,
-                                                            H, P, N, G, R, PB);
+                                                            H, P, N, G, R, PB, TB);
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;
 }
