@@ -205,6 +205,7 @@ __global__ void __launch_bounds__(128) kf_latent_query_kernel(float* __restrict_
         float s[QT];
 #pragma unroll
         for (int t = 0; t < QT; t++) s[t] = 0.f;
+#pragma unroll 8
         for (int d = 0; d < dn; d++) {
             const float w = bf16_bits_to_f32(Wuk[((size_t)h * dn + d) * rank + c]);
 #pragma unroll
@@ -479,16 +480,19 @@ __global__ void __launch_bounds__(128) kf_latent_merge_kernel(float* __restrict_
     const int m = blockIdx.x, h = blockIdx.y;
     const float* ml = part_ml + ((size_t)m * HG * 16 + h) * S * 2;
     const float* po = part_o + ((size_t)m * HG * 16 + h) * S * rank;
+    __shared__ float fac[64];  // exp(m_s - M) per split (S <= 64), 0 for an empty split
     const float sk = bf16_bits_to_f32(sink[h]);
     float M = sk;
     for (int s = 0; s < S; s++) M = fmaxf(M, ml[2 * s]);
+    if ((int)threadIdx.x < S) fac[threadIdx.x] = ml[2 * threadIdx.x] == -INFINITY ? 0.f : expf(ml[2 * threadIdx.x] - M);
+    __syncthreads();
     float den = expf(sk - M);
-    for (int s = 0; s < S; s++) den += ml[2 * s] == -INFINITY ? 0.f : ml[2 * s + 1] * expf(ml[2 * s] - M);
+    for (int s = 0; s < S; s++) den += ml[2 * s + 1] * fac[s];
     float* o = out + ((size_t)m * H + h) * rank;
     for (int c = threadIdx.x; c < rank; c += blockDim.x) {
         float v = 0.f;
-        for (int s = 0; s < S; s++)
-            if (ml[2 * s] != -INFINITY) v = fmaf(po[(size_t)s * rank + c], expf(ml[2 * s] - M), v);
+#pragma unroll 4
+        for (int s = 0; s < S; s++) v = fmaf(po[(size_t)s * rank + c], fac[s], v);
         o[c] = v / den;
     }
 }
@@ -501,6 +505,7 @@ __global__ void __launch_bounds__(256) kf_latent_expand_kernel(TO* __restrict__ 
     for (int e = warp; e < dv; e += 8) {
         const uint16_t* w = Wuv + ((size_t)h * dv + e) * rank;
         float s = 0.f;
+#pragma unroll 8
         for (int c = lane; c < rank; c += 32) s = fmaf(l[c], bf16_bits_to_f32(w[c]), s);
         s = warp_sum(s);
         if (lane == 0) {
