@@ -269,7 +269,7 @@ int kf_f32_to_bf16(kf_ctx* ctx, void* out_bf16_dev, const float* in_dev, size_t 
 int kf_moe_route(kf_ctx* ctx, int32_t* idx_dev, float* wgt_dev, int32_t* offsets_dev, int32_t* entry_slot_dev, int32_t* slot_row_dev,
                  int32_t* slot_group_dev, int32_t* work_dev, const float* logits_dev, int ldl, const void* bias_bf16_dev, int M, int E, int top);
 int kf_moe_combine(kf_ctx* ctx, float* out_dev, const float* y_slots_dev, const int32_t* entry_slot_dev, const float* wgt_dev, const float* shared_dev,
-                   const float* shared_gate_logit_dev, int M, int dim, int top);
+                   const float* shared_gate_logit_dev, int ld_gate /* stride between tokens' gate logits */, int M, int dim, int top);
 int kf_conv_silu(kf_ctx* ctx, float* xbc_out_dev, const float* u_dev, int ldu, int c0, const void* w_bf16_dev, const void* b_bf16_dev, float* tail_dev,
                  size_t tail_stride, const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int C, int K);
 int kf_ssm_scan(kf_ctx* ctx, float* y_dev, int ldy, const float* xbc_dev, const float* u_dev, int ldu, int dt_off, const void* dt_bias_bf16_dev,

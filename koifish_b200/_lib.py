@@ -105,7 +105,7 @@ SIGNATURES = {
     "kf_group_rmsnorm": (_I, [_P, _P, _I, _I, _P, _F, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _I, _F]),
     "kf_f32_to_bf16": (_I, [_P, _P, _P, _SZ]),
     "kf_moe_route": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I]),
-    "kf_moe_combine": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I]),
+    "kf_moe_combine": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I]),
     "kf_conv_silu": (_I, [_P, _P, _P, _I, _I, _P, _P, _P, _SZ, _P, _P, _I, _I, _I, _I]),
     "kf_ssm_scan": (_I, [_P, _P, _I, _P, _P, _I, _I, _P, _P, _P, _P, _SZ, _P, _P, _I, _I, _I, _I, _I, _I]),
     "kf_latent_append": (_I, [_P, _P, _I, _SZ, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F]),

@@ -221,6 +221,22 @@ static int BuildSipazen(Fish& f) {
             maxSF = std::max<size_t>(maxSF, mc.shared_ff);
             blk->moe = std::move(e);
         }
+        // stacked first projections of each sublayer
+        std::vector<hGTensor> c1 = {blk->rg1};
+        if (blk->ssm) c1.push_back(blk->ssm->in);
+        else c1.insert(c1.end(), {blk->attn->q, blk->attn->dkv, blk->attn->g});
+        blk->cat1.Plan(c1);
+        KF_TRY(b.Buf((char**)&blk->cat1.w, (size_t)blk->cat1.rows * E * 2));
+        KF_TRY(kf_memset(f.ctx, blk->cat1.w, 0, (size_t)blk->cat1.rows * E * 2));
+        maxU = std::max<size_t>(maxU, blk->cat1.rows);
+        if (blk->moe) {
+            std::vector<hGTensor> c2 = {blk->rg2, blk->moe->router};
+            if (blk->moe->sh_sg) c2.push_back(blk->moe->sh_sg);
+            blk->cat2.Plan(c2);
+            KF_TRY(b.Buf((char**)&blk->cat2.w, (size_t)blk->cat2.rows * E * 2));
+            KF_TRY(kf_memset(f.ctx, blk->cat2.w, 0, (size_t)blk->cat2.rows * E * 2));
+            maxU = std::max<size_t>(maxU, blk->cat2.rows);
+        }
         f.blocks.push_back(std::move(blk));
     }
     // activations: fp32 residual stream; matmul inputs in the activation type
@@ -263,6 +279,18 @@ static int BuildSipazen(Fish& f) {
     return KF_OK;
 }
 
+void StackedLinear::Plan(const std::vector<hGTensor>& tensors) {
+    parts = tensors, off.clear(), rows = 0, cols = tensors[0]->ne[1];
+    for (auto& t : parts) off.push_back(rows), rows += t->ne[0];
+    rows = (rows + 15) / 16 * 16;
+}
+int StackedLinear::Fill(kf_ctx* ctx) const {
+    for (size_t i = 0; i < parts.size(); i++) {
+        int rc = kf_d2d(ctx, (char*)w + (size_t)off[i] * cols * 2, parts[i]->data, (size_t)parts[i]->ne[0] * cols * 2);
+        if (rc) return rc;
+    }
+    return KF_OK;
+}
 // device pointer tables of the experts, once every tensor has its data
 int MoE::Prepare() {
     Fish& f = *hFish;
@@ -275,10 +303,10 @@ int MoE::Prepare() {
 static int PrepareSipazen(Fish& f) {
     for (auto& n : f.blocks) {
         HybridBlock* b = static_cast<HybridBlock*>(n.get());
-        if (b->moe) {
-            int rc = b->moe->Prepare();
-            if (rc) return rc;
-        }
+        int rc = b->cat1.Fill(f.ctx);
+        if (!rc && b->moe) rc = b->cat2.Fill(f.ctx);
+        if (!rc && b->moe) rc = b->moe->Prepare();
+        if (rc) return rc;
     }
     return KF_OK;
 }
@@ -289,27 +317,27 @@ static int Lin(Fish& f, float* y, const hGTensor& w, const void* x, int M) {
     return kf_linear_g(f.ctx, y, d.rows, &d, x, f.config.compute_f32 ? 1 : 0, d.cols, M);
 }
 
-int SSMixer::cuInfer(int M) {
+int SSMixer::cuInfer(int M, const float* u, int ldu, int off_in) {
     Fish& f = *hFish;
     std::string* hFishErr = &f.error;
     HybridScratch& s = *f.hscratch;
     const MIXER_CARD& m = card;
-    const int inner = m.heads * m.vdim, C = inner + 2 * m.groups * m.state, rows = in->ne[0];
+    const int inner = m.heads * m.vdim, C = inner + 2 * m.groups * m.state;
+    const float* ui = u + off_in;  // [z | x | B | C | dt] of every token, row stride ldu
     const int nseq = f.seq_mode ? M : 1, T = f.seq_mode ? 1 : M;
     const int ak = f.config.compute_f32 ? 1 : 0;
     SeqStateCache::Layer& sl = f.states.layers[layer];
-    KF_TRY(Lin(f, s.u, in, s.hact, M));  // [z | x | B | C | dt]
-    KF_TRY(kf_conv_silu(f.ctx, s.v, s.u, rows, inner, conv->data, conv_b->data, sl.tail, sl.tail_stride, f.d_pos, f.d_slot, nseq, T, C, m.conv));
-    KF_TRY(kf_ssm_scan(f.ctx, s.y, inner, s.v, s.u, rows, 2 * inner + 2 * m.groups * m.state, dt_bias->data, A_log->data, D->data, sl.state, sl.state_stride,
+    KF_TRY(kf_conv_silu(f.ctx, s.v, ui, ldu, inner, conv->data, conv_b->data, sl.tail, sl.tail_stride, f.d_pos, f.d_slot, nseq, T, C, m.conv));
+    KF_TRY(kf_ssm_scan(f.ctx, s.y, inner, s.v, ui, ldu, 2 * inner + 2 * m.groups * m.state, dt_bias->data, A_log->data, D->data, sl.state, sl.state_stride,
                        f.d_pos, f.d_slot, nseq, T, m.heads, m.vdim, m.state, m.groups));
     // y * silu(z), then RMS norm in norm_groups parts
-    KF_TRY(kf_group_rmsnorm(f.ctx, s.act, ak, inner, nullptr, 0.f, s.y, inner, s.u, rows, nullptr, 2, norm->data, nullptr, M, inner, m.norm_groups,
+    KF_TRY(kf_group_rmsnorm(f.ctx, s.act, ak, inner, nullptr, 0.f, s.y, inner, ui, ldu, nullptr, 2, norm->data, nullptr, M, inner, m.norm_groups,
                             f.config.norm_rms_eps));
     KF_TRY(Lin(f, s.sub, o, s.act, M));
     return KF_OK;
 }
 
-int LatentAttention::cuInfer(int M) {
+int LatentAttention::cuInfer(int M, const float* u, int ldu, int off_q, int off_dkv, int off_g) {
     Fish& f = *hFish;
     std::string* hFishErr = &f.error;
     HybridScratch& s = *f.hscratch;
@@ -317,26 +345,23 @@ int LatentAttention::cuInfer(int M) {
     const int ak = f.config.compute_f32 ? 1 : 0;
     SeqStateCache::Layer& sl = f.states.layers[layer];
     const int W = m.kv_rank + m.rot_dim;
-    KF_TRY(Lin(f, s.u, q, s.hact, M));
-    KF_TRY(Lin(f, s.v, dkv, s.hact, M));
-    KF_TRY(Lin(f, s.g, g, s.hact, M));
-    KF_TRY(kf_latent_append(f.ctx, sl.rows, ak, sl.row_stride, s.v, W, dkv_norm->data, inv_freq, f.d_pos, f.d_slot, M, m.kv_rank, m.rot_dim, m.rot_dims,
+    (void)W;
+    KF_TRY(kf_latent_append(f.ctx, sl.rows, ak, sl.row_stride, u + off_dkv, ldu, dkv_norm->data, inv_freq, f.d_pos, f.d_slot, M, m.kv_rank, m.rot_dim, m.rot_dims,
                             f.config.norm_rms_eps));
-    KF_TRY(kf_latent_attention(f.ctx, s.lat, s.y, s.u, q->ne[0], uk->data, sink->data, sl.rows, ak, sl.row_stride, inv_freq, f.d_pos, f.d_slot, M, m.heads,
+    KF_TRY(kf_latent_attention(f.ctx, s.lat, s.y, u + off_q, ldu, uk->data, sink->data, sl.rows, ak, sl.row_stride, inv_freq, f.d_pos, f.d_slot, M, m.heads,
                                m.dim, m.rot_dim, m.rot_dims, m.kv_rank, m.scale, f.attn_hint));
-    KF_TRY(kf_latent_expand(f.ctx, s.act, ak, s.lat, uv->data, s.g, m.heads * m.vdim, M, m.heads, m.vdim, m.kv_rank));
+    KF_TRY(kf_latent_expand(f.ctx, s.act, ak, s.lat, uv->data, u + off_g, ldu, M, m.heads, m.vdim, m.kv_rank));
     KF_TRY(Lin(f, s.sub, o, s.act, M));
     return KF_OK;
 }
 
-int MoE::cuInfer(int M) {
+int MoE::cuInfer(int M, const float* u, int ldu, int off_router, int off_sg) {
     Fish& f = *hFish;
     std::string* hFishErr = &f.error;
     HybridScratch& s = *f.hscratch;
     const int E = f.config.n_embd, X = card.experts, top = card.top;
     const int ak = f.config.compute_f32 ? 1 : 0;
-    KF_TRY(Lin(f, s.router, router, s.hact, M));
-    KF_TRY(kf_moe_route(f.ctx, s.idx, s.wgt, s.offsets, s.entry_slot, s.slot_row, s.slot_group, s.work, s.router, X, router_b->data, M, X, top));
+    KF_TRY(kf_moe_route(f.ctx, s.idx, s.wgt, s.offsets, s.entry_slot, s.slot_row, s.slot_group, s.work, u + off_router, ldu, router_b->data, M, X, top));
     const void* const* tb = (const void* const*)tables;
     KF_TRY(kf_linear_grouped(f.ctx, s.h1, card.ff, tb, tb + X, X, card.ff, E, s.hact, ak, E, s.offsets, s.slot_group, s.slot_row, M * top));
     KF_TRY(kf_linear_grouped(f.ctx, s.yslots, E, tb + 2 * X, nullptr, X, E, card.ff, s.h1, ak, card.ff, s.offsets, s.slot_group, nullptr, M * top));
@@ -345,9 +370,8 @@ int MoE::cuInfer(int M) {
         kf_tensor_desc dg = sh_gate->Desc(), du = sh_up->Desc();
         KF_TRY(kf_linear_g_swiglu(f.ctx, s.hs, card.shared_ff, &dg, &du, s.hact, ak, E, M));
         KF_TRY(Lin(f, s.shared, sh_down, s.hs, M));
-        KF_TRY(Lin(f, s.sg, sh_sg, s.hact, M));
     }
-    KF_TRY(kf_moe_combine(f.ctx, s.sub, s.yslots, s.entry_slot, s.wgt, sh ? s.shared : nullptr, sh ? s.sg : nullptr, M, E, top));
+    KF_TRY(kf_moe_combine(f.ctx, s.sub, s.yslots, s.entry_slot, s.wgt, sh ? s.shared : nullptr, sh ? u + off_sg : nullptr, ldu, M, E, top));
     return KF_OK;
 }
 
@@ -360,15 +384,20 @@ int HybridBlock::cuInfer(int M) {
     float* x = (float*)f.x;
     // h = norm1(x); sub = mixer(h); x += m * norm1b(sub * sigmoid(rg1 h + b))
     KF_TRY(kf_group_rmsnorm(f.ctx, s.hact, ak, E, nullptr, 0.f, x, E, nullptr, 0, nullptr, 0, norm1.w->data, nullptr, M, E, norm1.groups, norm1.eps));
-    KF_TRY(Lin(f, s.gate_logit, rg1, s.hact, M));
-    KF_TRY(ssm ? ssm->cuInfer(M) : attn->cuInfer(M));
-    KF_TRY(kf_group_rmsnorm(f.ctx, nullptr, 2, E, x, c.residual_mult, s.sub, E, s.gate_logit, E, rg1_b->data, 1, norm1b.w->data, nullptr, M, E, norm1b.groups,
+    // one matmul for everything that reads h: the residual gate's logits (columns 0 .. E) and the mixer's first projections
+    kf_tensor_desc d1 = {};
+    d1.data_dev = cat1.w, d1.rows = cat1.rows, d1.cols = cat1.cols, d1.type = KF_T_BF16, d1.group = 128;
+    KF_TRY(kf_linear_g(f.ctx, s.u, cat1.rows, &d1, s.hact, ak, E, M));
+    KF_TRY(ssm ? ssm->cuInfer(M, s.u, cat1.rows, cat1.off[1]) : attn->cuInfer(M, s.u, cat1.rows, cat1.off[1], cat1.off[2], cat1.off[3]));
+    KF_TRY(kf_group_rmsnorm(f.ctx, nullptr, 2, E, x, c.residual_mult, s.sub, E, s.u, cat1.rows, rg1_b->data, 1, norm1b.w->data, nullptr, M, E, norm1b.groups,
                             norm1b.eps));
     if (moe) {
         KF_TRY(kf_group_rmsnorm(f.ctx, s.hact, ak, E, nullptr, 0.f, x, E, nullptr, 0, nullptr, 0, norm2.w->data, nullptr, M, E, norm2.groups, norm2.eps));
-        KF_TRY(Lin(f, s.gate_logit, rg2, s.hact, M));
-        KF_TRY(moe->cuInfer(M));
-        KF_TRY(kf_group_rmsnorm(f.ctx, nullptr, 2, E, x, c.residual_mult, s.sub, E, s.gate_logit, E, rg2_b->data, 1, norm2b.w->data, nullptr, M, E,
+        kf_tensor_desc d2 = {};
+        d2.data_dev = cat2.w, d2.rows = cat2.rows, d2.cols = cat2.cols, d2.type = KF_T_BF16, d2.group = 128;
+        KF_TRY(kf_linear_g(f.ctx, s.u, cat2.rows, &d2, s.hact, ak, E, M));
+        KF_TRY(moe->cuInfer(M, s.u, cat2.rows, cat2.off[1], cat2.off.size() > 2 ? cat2.off[2] : 0));
+        KF_TRY(kf_group_rmsnorm(f.ctx, nullptr, 2, E, x, c.residual_mult, s.sub, E, s.u, cat2.rows, rg2_b->data, 1, norm2b.w->data, nullptr, M, E,
                                 norm2b.groups, norm2b.eps));
     }
     return KF_OK;

@@ -31,6 +31,16 @@ struct HybridScratch {  // device buffers shared by all layers, sized for max_to
     void* head_in = nullptr;     // final norm of the selected rows, activation type
 };
 
+// Several weights that read the same normed input, stacked row-wise into ONE matrix at load (rows padded to a multiple of 16 so that the
+// tuned kernels take it): one launch instead of one per weight; consumers read their columns of the result at off[i] with stride `rows`.
+struct StackedLinear {
+    void* w = nullptr;  // device bf16 [rows][cols]
+    int rows = 0, cols = 0;
+    std::vector<hGTensor> parts;
+    std::vector<int> off;
+    void Plan(const std::vector<hGTensor>& tensors);  // sizes only
+    int Fill(kf_ctx* ctx) const;                      // copy the parts' rows (after every tensor has data)
+};
 struct GroupNorm : GeNeuron {
     hGTensor w;
     int groups = 1;
@@ -40,14 +50,14 @@ struct SSMixer : GeNeuron {
     MIXER_CARD card;
     int layer = 0;
     hGTensor in, conv, conv_b, dt_bias, A_log, D, norm, o;
-    int cuInfer(int M);  // hact -> sub
+    int cuInfer(int M, const float* u, int ldu, int off_in);  // u: stacked first projections; in-projection at column off_in; -> sub
 };
 struct LatentAttention : GeNeuron {
     MIXER_CARD card;
     int layer = 0;
     hGTensor q, dkv, dkv_norm, uk, uv, sink, g, o;
     float* inv_freq = nullptr;  // device [rot_dims / 2]
-    int cuInfer(int M);
+    int cuInfer(int M, const float* u, int ldu, int off_q, int off_dkv, int off_g);
 };
 struct MoE : GeNeuron {
     MOE_CARD card;
@@ -56,12 +66,13 @@ struct MoE : GeNeuron {
     hGTensor sh_gate, sh_up, sh_down, sh_sg;
     void** tables = nullptr;  // device: [3][experts] weight pointers (gate | up | down)
     int Prepare();
-    int cuInfer(int M);
+    int cuInfer(int M, const float* u, int ldu, int off_router, int off_sg);
 };
 struct HybridBlock : GeNeuron {
     int layer = 0;
     GroupNorm norm1, norm1b, norm2, norm2b;
     hGTensor rg1, rg1_b, rg2, rg2_b;
+    StackedLinear cat1, cat2;  // [rg1 | the mixer's first projections], [rg2 | router | shared-expert gate]
     std::unique_ptr<SSMixer> ssm;
     std::unique_ptr<LatentAttention> attn;
     std::unique_ptr<MoE> moe;
