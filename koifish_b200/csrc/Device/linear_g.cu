@@ -8,6 +8,8 @@
 // Two kernels: a warp-per-output GEMV for a handful of rows (decode: every weight row is read once, 16-byte loads when the row length
 // allows) and a 64 x 64 x 32 shared-memory tile kernel for panels (mma.sync m16n8k16 for bf16 activations, FFMA for float ones).
 // No reference equivalent: the reference's SLP::Forw hands every shape to cuBLASLt (src/Device/CUDA/NeuronFuse.cu:305-381).
+#include <algorithm>
+
 #include "kf_common.cuh"
 
 namespace {
@@ -133,9 +135,9 @@ __global__ void __launch_bounds__(256) kf_lin_tile_kernel(LinArgs a) {
     const int g    = blockIdx.z;
     const int lo   = a.offsets ? a.offsets[g] : 0;
     const int hi   = a.offsets ? a.offsets[g + 1] : a.M;
-    const int m0   = lo + blockIdx.y * BM;
-    if (m0 >= hi) return;
     const int n0 = blockIdx.x * BN;
+    // a CTA walks the slot tiles blockIdx.y, blockIdx.y + gridDim.y, ... of its group: the grid is sized for the average group, not the worst
+    for (int m0 = lo + blockIdx.y * BM; m0 < hi; m0 += gridDim.y * BM) {
     const uint16_t* W0 = a.Wt0 ? a.Wt0[g] : a.W0;
     const uint16_t* W1 = DUAL ? (a.Wt1 ? a.Wt1[g] : a.W1) : nullptr;
     constexpr bool MMA = sizeof(TA) == 2;
@@ -251,6 +253,8 @@ __global__ void __launch_bounds__(256) kf_lin_tile_kernel(LinArgs a) {
 #pragma unroll
             for (int j = 0; j < 4; j++) store(tr * 4 + i, n0 + tc * 4 + j, acc0[i * 4 + j], DUAL ? acc1[i * 4 + j] : 0.f);
     }
+    __syncthreads();  // the shared tiles are free for the next slot tile
+    }
 }
 
 template <typename TA, bool DUAL>
@@ -259,7 +263,9 @@ int launch(kf_ctx* ctx, const LinArgs& a, int slots, int groups, bool gemv) {
         dim3 grid((a.N + 7) / 8, slots);
         kf_lin_gemv_kernel<TA, DUAL><<<grid, 256, 0, ctx->stream>>>(a);
     } else {
-        dim3 grid((a.N + BN - 1) / BN, (slots + BM - 1) / BM, groups);
+        const int tiles = (slots + BM - 1) / BM;
+        const int gy    = groups > 1 ? std::min(tiles, std::max(1, (2 * slots / groups + BM - 1) / BM)) : tiles;
+        dim3 grid((a.N + BN - 1) / BN, gy, groups);
         kf_lin_tile_kernel<TA, DUAL><<<grid, 256, 0, ctx->stream>>>(a);
     }
     KF_LAUNCH_CHECK(ctx);
