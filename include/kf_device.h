@@ -276,9 +276,9 @@ int kf_ssm_scan(kf_ctx* ctx, float* y_dev, int ldy, const float* xbc_dev, const 
                 const void* A_log_bf16_dev, const void* D_bf16_dev, float* state_dev, size_t state_stride, const int32_t* pos_dev,
                 const int32_t* slot_dev, int nseq, int T, int H, int P, int N, int G);
 int kf_latent_append(kf_ctx* ctx, void* cache_dev, int cache_f32, size_t slot_stride, const float* ckr_dev, int ldc, const void* norm_w_bf16_dev,
-                     const float* inv_freq_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int rank, int rot_dim, int rot_dims, float eps);
+                     const double* inv_freq_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int rank, int rot_dim, int rot_dims, float eps);
 int kf_latent_attention(kf_ctx* ctx, float* lat_out_dev, float* qa_work_dev, const float* q_dev, int ldq, const void* w_uk_bf16_dev,
-                        const void* sink_bf16_dev, const void* cache_dev, int cache_f32, size_t slot_stride, const float* inv_freq_dev,
+                        const void* sink_bf16_dev, const void* cache_dev, int cache_f32, size_t slot_stride, const double* inv_freq_dev,
                         const int32_t* pos_dev, const int32_t* slot_dev, int M, int H, int dn, int rot_dim, int rot_dims, int rank, float scale,
                         int max_pos_hint /* upper bound of pos[]: sizes the split of the keys over CTAs */);
 int kf_latent_expand(kf_ctx* ctx, void* out_dev, int out_f32, const float* lat_dev, const void* w_uv_bf16_dev, const float* gate_logit_dev, int ldg,

@@ -152,11 +152,11 @@ __global__ void __launch_bounds__(1024) kf_ssm_scan_kernel(float* __restrict__ y
 
 // ------------------------------------------------------------------------------------------------------------ latent attention
 // cache row = [c (rank) | rotated shared key (rot_dim)].  One block per token: RMS norm of the first `rank` entries of the down
-// projection times w; rotate-half on the first `dims` entries of the rest (pair i <-> i + dims/2, angle pos * inv_freq[i], fp32 angle,
+// projection times w; rotate-half on the first `dims` entries of the rest (pair i <-> i + dims/2, angle pos * inv_freq[i] formed in double,
 // sine / cosine evaluated in double).
 template <typename TC>
 __global__ void __launch_bounds__(256) kf_latent_append_kernel(TC* __restrict__ cache, size_t slot_stride, const float* __restrict__ ckr, int ldc,
-                                                               const uint16_t* __restrict__ w, const float* __restrict__ inv_freq,
+                                                               const uint16_t* __restrict__ w, const double* __restrict__ inv_freq,
                                                                const int32_t* __restrict__ pos, const int32_t* __restrict__ slot, int rank, int rot_dim,
                                                                int dims, float eps) {
     __shared__ float red[32];
@@ -178,9 +178,8 @@ __global__ void __launch_bounds__(256) kf_latent_append_kernel(TC* __restrict__ 
         float v = in[rank + i];
         if (i < dims) {
             const int j = i < half ? i : i - half;
-            const float ang = fp * inv_freq[j];
             double sn, cs;
-            sincos((double)ang, &sn, &cs);
+            sincos((double)fp * inv_freq[j], &sn, &cs);  // angle, sine and cosine in double
             const float a = in[rank + j], b = in[rank + j + half];
             v = i < half ? a * (float)cs - b * (float)sn : b * (float)cs + a * (float)sn;
         }
@@ -191,7 +190,7 @@ __global__ void __launch_bounds__(256) kf_latent_append_kernel(TC* __restrict__ 
 // read once serves QT tokens
 constexpr int QT = 8;
 __global__ void __launch_bounds__(128) kf_latent_query_kernel(float* __restrict__ qa, const float* __restrict__ q, int ldq, const uint16_t* __restrict__ Wuk,
-                                                              const float* __restrict__ inv_freq, const int32_t* __restrict__ pos, int M, int H, int dn,
+                                                              const double* __restrict__ inv_freq, const int32_t* __restrict__ pos, int M, int H, int dn,
                                                               int rot_dim, int dims, int rank, float scale) {
     extern __shared__ float sq[];  // [QT][dn + rot_dim]
     const int m0 = blockIdx.x * QT, h = blockIdx.y, D = dn + rot_dim, W = rank + rot_dim;
@@ -222,9 +221,8 @@ __global__ void __launch_bounds__(128) kf_latent_query_kernel(float* __restrict_
         float v = sr[e];
         if (e < dims) {
             const int j = e < half ? e : e - half;
-            const float ang = (float)pos[m0 + t] * inv_freq[j];
             double sn, cs;
-            sincos((double)ang, &sn, &cs);
+            sincos((double)pos[m0 + t] * inv_freq[j], &sn, &cs);
             const float a = sr[j], b = sr[j + half];
             v = e < half ? a * (float)cs - b * (float)sn : b * (float)cs + a * (float)sn;
         }
@@ -559,7 +557,7 @@ extern "C" int kf_ssm_scan(kf_ctx* ctx, float* y, int ldy, const float* xbc, con
 }
 
 extern "C" int kf_latent_append(kf_ctx* ctx, void* cache, int cache_f32, size_t slot_stride, const float* ckr, int ldc, const void* norm_w_bf16,
-                                const float* inv_freq_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int rank, int rot_dim, int rot_dims,
+                                const double* inv_freq_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int rank, int rot_dim, int rot_dims,
                                 float eps) {
     if (!ctx || !cache || !ckr || !norm_w_bf16 || !inv_freq_dev || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, M >= 1 && rank >= 1 && rot_dim >= 0 && rot_dims >= 0 && rot_dims <= rot_dim && rot_dims % 2 == 0, "rotated dims: even, <= rot_dim");
@@ -575,7 +573,7 @@ extern "C" int kf_latent_append(kf_ctx* ctx, void* cache, int cache_f32, size_t 
 // lat_out [M][H][rank]: attention of every (token, head) over the rows 0 .. pos[m] of its slot.  q: float [M][ldq], heads laid out as
 // [dn plain | rot_dim rotated]; w_uk bf16 [H*dn][rank]; sink bf16 [H]; qa_work: float scratch [M][H][rank + rot_dim].
 extern "C" int kf_latent_attention(kf_ctx* ctx, float* lat_out, float* qa_work, const float* q, int ldq, const void* w_uk_bf16, const void* sink_bf16,
-                                   const void* cache, int cache_f32, size_t slot_stride, const float* inv_freq_dev, const int32_t* pos_dev,
+                                   const void* cache, int cache_f32, size_t slot_stride, const double* inv_freq_dev, const int32_t* pos_dev,
                                    const int32_t* slot_dev, int M, int H, int dn, int rot_dim, int rot_dims, int rank, float scale, int max_pos_hint) {
     if (!ctx || !lat_out || !qa_work || !q || !w_uk_bf16 || !sink_bf16 || !cache || !inv_freq_dev || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, M >= 1 && H >= 1 && dn >= 1 && rank >= 1 && rank + rot_dim <= 32 * LMAX && rot_dims <= rot_dim && rot_dims % 2 == 0, "rank + rot_dim <= 640");

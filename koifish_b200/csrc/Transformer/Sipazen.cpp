@@ -181,11 +181,11 @@ static int BuildSipazen(Fish& f) {
             b.Tensor(p + "mix.sink", 1, m.heads, a->sink);
             b.Tensor(p + "mix.g", m.heads * m.vdim, E, a->g);
             b.Tensor(p + "mix.o", E, m.heads * m.vdim, a->o);
-            // rotation frequencies base^(-2i/dims), evaluated in double and rounded once
-            std::vector<float> fr((size_t)std::max(1, m.rot_dims / 2));
-            for (int k = 0; k < m.rot_dims / 2; k++) fr[k] = (float)std::pow(m.rot_base, -2.0 * k / (double)m.rot_dims);
-            KF_TRY(b.Buf(&a->inv_freq, fr.size() * 4));
-            KF_TRY(kf_h2d(f.ctx, a->inv_freq, fr.data(), fr.size() * 4));
+            // rotation frequencies base^(-2i/dims) in double: the angle pos * f_i and its sine / cosine are formed in double on the device
+            std::vector<double> fr((size_t)std::max(1, m.rot_dims / 2));
+            for (int k = 0; k < m.rot_dims / 2; k++) fr[k] = std::pow(m.rot_base, -2.0 * k / (double)m.rot_dims);
+            KF_TRY(b.Buf(&a->inv_freq, fr.size() * 8));
+            KF_TRY(kf_h2d(f.ctx, a->inv_freq, fr.data(), fr.size() * 8));
             KF_TRY(kf_ctx_sync(f.ctx));
             sl.row_dim = W, sl.row_stride = (size_t)c.max_seq_len * W;
             KF_TRY(b.Buf((char**)&sl.rows, (size_t)c.max_batch * sl.row_stride * asz));

@@ -56,7 +56,7 @@ struct LatentAttention : GeNeuron {
     MIXER_CARD card;
     int layer = 0;
     hGTensor q, dkv, dkv_norm, uk, uv, sink, g, o;
-    float* inv_freq = nullptr;  // device [rot_dims / 2]
+    double* inv_freq = nullptr;  // device [rot_dims / 2]
     int cuInfer(int M, const float* u, int ldu, int off_q, int off_dkv, int off_g);
 };
 struct MoE : GeNeuron {
