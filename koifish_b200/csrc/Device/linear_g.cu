@@ -94,11 +94,11 @@ __global__ void __launch_bounds__(256) kf_lin_gemv_kernel(LinArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------------------------------ tile kernel
-// 64 slots x 64 outputs per CTA, k in steps of 32; 256 threads.  Float activations: each thread a 4 x 4 block of FFMA accumulators.
+// 64 slots x 64 outputs per CTA, k in steps of 64 (bf16) or 32 (float); 256 threads.  Float activations: each thread a 4 x 4 block of FFMA accumulators.
 // bf16 activations: 8 warps as 4 (m) x 2 (n), each warp 16 x 32 through mma.sync.m16n8k16; operands come from the same shared tiles.
 // The next k step's operands are fetched into registers (16-byte loads when the row length and alignment allow, else element by
 // element) while the current one is multiplied.  Every load is bounds-checked, so M, N and K are free.
-constexpr int BM = 64, BN = 64, BK = 32;
+constexpr int BM = 64, BN = 64;  // k step: 64 for bf16 activations (two 16-byte fetches per operand and thread in flight), 32 for float
 
 __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, const uint32_t* b) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(256) kf_lin_tile_kernel(LinArgs a) {
     const uint16_t* W0 = a.Wt0 ? a.Wt0[g] : a.W0;
     const uint16_t* W1 = DUAL ? (a.Wt1 ? a.Wt1[g] : a.W1) : nullptr;
     constexpr bool MMA = sizeof(TA) == 2;
+    constexpr int BK  = MMA ? 64 : 32, NF = BK / 32;
     constexpr int LDS = BK + 8;  // row pitch in elements: 16-byte aligned rows, conflict-free fragment loads
     __shared__ __align__(16) TA sx[BM][LDS];
     __shared__ __align__(16) uint16_t sw0[BN][LDS];
@@ -165,27 +166,33 @@ __global__ void __launch_bounds__(256) kf_lin_tile_kernel(LinArgs a) {
     const int warp = tid >> 5, lane = tid & 31;
     const int wm = warp & 3, wn = warp >> 2;      // MMA: warp tile rows wm*16, cols wn*32
     const int tr = tid >> 4, tc = tid & 15;        // FFMA: thread rows tr*4.., cols tc*4..
-    Frag8<TA> fx;
-    Frag8<uint16_t> fw0, fw1;
-    fetch8<TA>(fx, (const TA*)a.x, xoff, lk, a.K, xrow >= 0, xvec);
-    fetch8<uint16_t>(fw0, W0, woff, lk, a.K, wok, wvec);
-    if (DUAL) fetch8<uint16_t>(fw1, W1, woff, lk, a.K, wok, wvec);
+    Frag8<TA> fx[NF];
+    Frag8<uint16_t> fw0[NF], fw1[NF];
+    auto fetch = [&](int kb) {  // fragment f covers k = kb + f * 32 + lk .. + 7
+#pragma unroll
+        for (int f = 0; f < NF; f++) {
+            fetch8<TA>(fx[f], (const TA*)a.x, xoff, kb + f * 32 + lk, a.K, xrow >= 0, xvec);
+            fetch8<uint16_t>(fw0[f], W0, woff, kb + f * 32 + lk, a.K, wok, wvec);
+            if (DUAL) fetch8<uint16_t>(fw1[f], W1, woff, kb + f * 32 + lk, a.K, wok, wvec);
+        }
+    };
+    fetch(0);
     for (int k0 = 0; k0 < a.K; k0 += BK) {
         __syncthreads();  // the previous step's fragments have been read
-        if (MMA) {
-            *reinterpret_cast<uint4*>(&sx[lr][lk]) = *reinterpret_cast<const uint4*>(fx.v);
-        } else {
-            *reinterpret_cast<float4*>(&sx[lr][lk])     = *reinterpret_cast<const float4*>(fx.v);
-            *reinterpret_cast<float4*>(&sx[lr][lk + 4]) = *reinterpret_cast<const float4*>(fx.v + 4);
+#pragma unroll
+        for (int f = 0; f < NF; f++) {
+            const int kc = f * 32 + lk;
+            if (MMA) {
+                *reinterpret_cast<uint4*>(&sx[lr][kc]) = *reinterpret_cast<const uint4*>(fx[f].v);
+            } else {
+                *reinterpret_cast<float4*>(&sx[lr][kc])     = *reinterpret_cast<const float4*>(fx[f].v);
+                *reinterpret_cast<float4*>(&sx[lr][kc + 4]) = *reinterpret_cast<const float4*>(fx[f].v + 4);
+            }
+            *reinterpret_cast<uint4*>(&sw0[lr][kc]) = *reinterpret_cast<const uint4*>(fw0[f].v);
+            if (DUAL) *reinterpret_cast<uint4*>(&sw1[lr][kc]) = *reinterpret_cast<const uint4*>(fw1[f].v);
         }
-        *reinterpret_cast<uint4*>(&sw0[lr][lk]) = *reinterpret_cast<const uint4*>(fw0.v);
-        if (DUAL) *reinterpret_cast<uint4*>(&sw1[lr][lk]) = *reinterpret_cast<const uint4*>(fw1.v);
         __syncthreads();
-        if (k0 + BK < a.K) {  // next step's operands travel while this one is multiplied
-            fetch8<TA>(fx, (const TA*)a.x, xoff, k0 + BK + lk, a.K, xrow >= 0, xvec);
-            fetch8<uint16_t>(fw0, W0, woff, k0 + BK + lk, a.K, wok, wvec);
-            if (DUAL) fetch8<uint16_t>(fw1, W1, woff, k0 + BK + lk, a.K, wok, wvec);
-        }
+        if (k0 + BK < a.K) fetch(k0 + BK);  // next step's operands travel while this one is multiplied
         if (MMA) {
             // fragments through ldmatrix: A = 16 rows x 16 k of this warp's slots; B = two 8-output tiles per instruction
             const uint16_t* xa = (const uint16_t*)&sx[wm * 16][0];
