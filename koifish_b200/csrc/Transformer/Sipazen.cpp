@@ -131,7 +131,7 @@ static int BuildSipazen(Fish& f) {
     const size_t T = f.max_tokens;
     auto hs = std::make_shared<HybridScratch>();
     f.hscratch = hs;
-    size_t maxU = 1, maxV = 1, maxY = 1, maxL = 1, maxG = 1, maxA = 1, maxE = 1, maxTop = 1, maxFF = 1, maxSF = 1;
+    size_t maxU = 1, maxV = 1, maxY = 1, maxL = 1, maxA = 1, maxE = 1, maxTop = 1, maxFF = 1, maxSF = 1;
     f.states.layers.resize(c.layers.size());
     f.states.max_seq = c.max_seq_len, f.states.f32 = f32;
     for (size_t i = 0; i < c.layers.size(); i++) {
@@ -167,7 +167,7 @@ static int BuildSipazen(Fish& f) {
             KF_TRY(b.Buf(&sl.state, (size_t)c.max_batch * sl.state_stride * 4));
             KF_TRY(b.Buf(&sl.tail, (size_t)c.max_batch * sl.tail_stride * 4));
             f.states.total_bytes += (size_t)c.max_batch * (sl.state_stride + sl.tail_stride) * 4;
-            maxU = std::max<size_t>(maxU, rows), maxV = std::max<size_t>(maxV, C), maxY = std::max<size_t>(maxY, inner), maxA = std::max<size_t>(maxA, inner);
+            maxV = std::max<size_t>(maxV, C), maxY = std::max<size_t>(maxY, inner), maxA = std::max<size_t>(maxA, inner);
             blk->ssm = std::move(s);
         } else {
             auto a = std::make_unique<LatentAttention>();
@@ -190,8 +190,8 @@ static int BuildSipazen(Fish& f) {
             sl.row_dim = W, sl.row_stride = (size_t)c.max_seq_len * W;
             KF_TRY(b.Buf((char**)&sl.rows, (size_t)c.max_batch * sl.row_stride * asz));
             f.states.total_bytes += (size_t)c.max_batch * sl.row_stride * asz;
-            maxU = std::max<size_t>(maxU, qd), maxV = std::max<size_t>(maxV, W), maxY = std::max<size_t>(maxY, (size_t)m.heads * W);
-            maxL = std::max<size_t>(maxL, (size_t)m.heads * m.kv_rank), maxG = std::max<size_t>(maxG, (size_t)m.heads * m.vdim);
+            maxV = std::max<size_t>(maxV, W), maxY = std::max<size_t>(maxY, (size_t)m.heads * W);
+            maxL = std::max<size_t>(maxL, (size_t)m.heads * m.kv_rank);
             maxA = std::max<size_t>(maxA, (size_t)m.heads * m.vdim);
             blk->attn = std::move(a);
         }
@@ -242,15 +242,12 @@ static int BuildSipazen(Fish& f) {
     // activations: fp32 residual stream; matmul inputs in the activation type
     KF_TRY(kf_malloc(f.ctx, T * E * 4, &f.x));
     KF_TRY(b.Buf((char**)&hs->hact, T * E * asz));
-    KF_TRY(b.Buf(&hs->gate_logit, T * E * 4));
     KF_TRY(b.Buf(&hs->sub, T * E * 4));
     KF_TRY(b.Buf(&hs->u, T * maxU * 4));
     KF_TRY(b.Buf(&hs->v, T * maxV * 4));
     KF_TRY(b.Buf(&hs->y, T * maxY * 4));
     KF_TRY(b.Buf(&hs->lat, T * maxL * 4));
-    KF_TRY(b.Buf(&hs->g, T * maxG * 4));
     KF_TRY(b.Buf((char**)&hs->act, T * maxA * asz));
-    KF_TRY(b.Buf(&hs->router, T * maxE * 4));
     const size_t TT = T * maxTop;
     KF_TRY(b.Buf(&hs->idx, TT * 4));
     KF_TRY(b.Buf(&hs->wgt, TT * 4));
@@ -263,7 +260,6 @@ static int BuildSipazen(Fish& f) {
     KF_TRY(b.Buf(&hs->yslots, TT * E * 4));
     KF_TRY(b.Buf((char**)&hs->hs, T * maxSF * asz));
     KF_TRY(b.Buf(&hs->shared, T * E * 4));
-    KF_TRY(b.Buf(&hs->sg, T * 4));
     KF_TRY(b.Buf((char**)&hs->head_in, (size_t)f.logit_rows * E * asz));
     KF_TRY(kf_malloc(f.ctx, (size_t)f.logit_rows * c.vocab * 2, &f.logits));
     KF_TRY(kf_malloc(f.ctx, (size_t)f.logit_rows * c.vocab * 4, (void**)&f.logits_f32));

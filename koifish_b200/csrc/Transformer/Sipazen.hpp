@@ -11,23 +11,19 @@ namespace koifish {
 
 struct HybridScratch {  // device buffers shared by all layers, sized for max_tokens
     void* hact = nullptr;        // normed input of a sublayer, activation type [T][E]
-    float* gate_logit = nullptr; // residual-gate logits [T][E]
     float* sub = nullptr;        // sublayer result [T][E]
-    float* u = nullptr;          // widest first projection (state-space in-projection / attention queries)
+    float* u = nullptr;          // result of a sublayer's stacked first projections [T][widest stack]: gate logits | in-projection or q | dkv | g ...
     float* v = nullptr;          // convolution output / latent down-projection
     float* y = nullptr;          // scan output / absorbed queries
     float* lat = nullptr;        // attended latent [T][H][rank]
-    float* g = nullptr;          // attention output-gate logits
     void* act = nullptr;         // input of the output projection, activation type
     // mixture of experts
-    float* router = nullptr;     // [T][E]
     int32_t *idx = nullptr, *offsets = nullptr, *entry_slot = nullptr, *slot_row = nullptr, *slot_group = nullptr, *work = nullptr;
     float* wgt = nullptr;
     void* h1 = nullptr;          // [T * top][ff] activation type
     float* yslots = nullptr;     // [T * top][E]
     void* hs = nullptr;          // shared expert hidden, activation type
     float* shared = nullptr;     // [T][E]
-    float* sg = nullptr;         // [T]
     void* head_in = nullptr;     // final norm of the selected rows, activation type
 };
 
