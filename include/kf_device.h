@@ -284,6 +284,51 @@ int kf_latent_attention(kf_ctx* ctx, float* lat_out_dev, float* qa_work_dev, con
 int kf_latent_expand(kf_ctx* ctx, void* out_dev, int out_f32, const float* lat_dev, const void* w_uv_bf16_dev, const float* gate_logit_dev, int ldg,
                      int M, int H, int dv, int rank);
 
+
+/* ---- more mechanisms for stacks with a 32-bit residual (ops_f32.cu, seqmix.cu, linrec.cu, attn_bias.cu); no reference equivalents ---- */
+/* out[m] = scale * W[token[m]] as floats; out2 (optional) receives a second copy */
+int kf_embed_f32_scaled(kf_ctx* ctx, float* out_dev, float* out2_dev, const kf_tensor_desc* w, const int32_t* tokens_dev, int M, float scale);
+/* out[rows][ldo] = act(in[rows][ldi] + bias) (* mul); act 0: none, 1: gelu (tanh form), 2: relu squared, 3: silu; out_kind 0: bf16 bits,
+ * 1: float, 2: float out += result */
+int kf_bias_act(kf_ctx* ctx, void* out_dev, int out_kind, int ldo, const float* in_dev, int ldi, const void* bias_bf16_dev, int act, const float* mul_dev,
+                int ldm, int rows, int cols);
+/* out[r][c] = gelu_tanh(in[r][c]) * table[token[r]][c0 + c], in the activation type */
+int kf_token_gate(kf_ctx* ctx, void* out_dev, int out_f32, int ldo, const float* in_dev, int ldi, const void* table_bf16_dev, int ldt, int c0,
+                  const int32_t* tokens_dev, int rows, int cols);
+/* hist[n_prev] = x ; x = sum_{j <= n_prev} w[j] * hist[j]   (weighted sum over the depth of a stack; w bf16 [n_prev + 1]) */
+int kf_depth_mix(kf_ctx* ctx, float* x_dev, float* hist_dev, size_t hist_stride, const void* w_bf16_dev, int n_prev, size_t n);
+/* kf_group_rmsnorm with two more gate kinds (3 / 4: sigmoid(gate) / silu(gate) multiply the normed result) and a weight of group size
+ * shared by all groups (w_shared) */
+int kf_group_rmsnorm_ex(kf_ctx* ctx, void* out_dev, int out_kind, int ldo, float* res_dev, float mult, const float* x_dev, int ldx, const float* gate_dev,
+                        int ldg, const void* gate_bias_bf16_dev, int gate_kind, const void* w_bf16_dev, int w_shared, const int32_t* row_idx_dev, int rows,
+                        int dim, int groups, float eps);
+/* kf_moe_route with a choice of weights: full_softmax 1 = the chosen entries of the softmax over all experts, not renormalised */
+int kf_moe_route_ex(kf_ctx* ctx, int32_t* idx_dev, float* wgt_dev, int32_t* offsets_dev, int32_t* entry_slot_dev, int32_t* slot_row_dev,
+                    int32_t* slot_group_dev, int32_t* work_dev, const float* logits_dev, int ldl, const void* bias_bf16_dev, int M, int E, int top,
+                    int full_softmax);
+/* kf_linear_grouped with an activation on the result written in the activation type: act 2 = relu squared (0: float result, no activation) */
+int kf_linear_grouped_act(kf_ctx* ctx, void* y_dev, int ldy, const void* const* w_table_dev, int n_groups, int N, int K, const void* x_dev, int act_f32,
+                          int ldx, const int32_t* offsets_dev, const int32_t* slot_group_dev, const int32_t* src_row_dev, int slots, int act);
+/* kf_conv_silu with the activation as a parameter (0: none, 1: SiLU) */
+int kf_conv1d(kf_ctx* ctx, float* out_dev, const float* u_dev, int ldu, int c0, const void* w_bf16_dev, const void* b_bf16_dev, float* tail_dev,
+              size_t tail_stride, const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int C, int K, int act);
+/* matrix-state recurrence with a decay per key channel: gated linear attention (delta 0) or the gated delta rule (delta 1) */
+int kf_gated_scan(kf_ctx* ctx, float* y_dev, int ldy, const float* q_dev, int ldq, const float* k_dev, int ldk, const float* v_dev, int ldv,
+                  const float* z_dev, int ldz, const void* zbias_bf16_dev, const void* A_log_bf16_dev, const float* beta_logit_dev, int ldb, float* state_dev,
+                  size_t state_stride, const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int H, int G, int dk, int dv, int delta,
+                  int decay_kind, float tau, int unit_qk, float unit_eps, float q_scale);
+/* real-gated linear recurrent unit over channels (block-diagonal gates) */
+int kf_rglru(kf_ctx* ctx, void* out_dev, int out_f32, int ldo, float* work_dev, const float* u_dev, int ldu, const void* w_r_bf16_dev,
+             const void* b_r_bf16_dev, const void* w_i_bf16_dev, const void* b_i_bf16_dev, const void* lam_bf16_dev, float decay_c, const float* y_logit_dev,
+             int ldy, const void* y_bias_bf16_dev, float* state_dev, size_t state_stride, const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T,
+             int width, int blocks);
+/* key / value rows into a per-slot cache, and causal grouped-query attention with a logarithmic distance penalty and a query temperature */
+int kf_kv_append(kf_ctx* ctx, void* cache_dev, int cache_f32, size_t slot_stride, const float* k_dev, int ldk, int nk, const float* v_dev, int ldv, int nv,
+                 const int32_t* pos_dev, const int32_t* slot_dev, int M);
+int kf_attn_bias(kf_ctx* ctx, void* out_dev, int out_f32, int ldo, const float* q_dev, int ldq, const float* gate_logit_dev, int ldg, const void* cache_dev,
+                 int cache_f32, size_t slot_stride, const void* r1_bf16_dev, const void* r2_bf16_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M,
+                 int H, int G, int dk, int dv, float scale, float t_coef, int t_every);
+
 #ifdef __cplusplus
 }
 #endif

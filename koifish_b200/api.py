@@ -769,6 +769,21 @@ def kun_write(path, config, tensors):
         raise KoifishError(st, "kf_kun_write", _take_string(lib, err) if err.value else "")
 
 
+def _safetensors_shapes(model_dir):
+    """name -> shape of every tensor in the folder's *.safetensors files (headers only: 8-byte length, then that many bytes of JSON)."""
+    import glob
+    import os
+    import struct
+    shapes = {}
+    for path in sorted(glob.glob(os.path.join(model_dir, "*.safetensors"))):
+        with open(path, "rb") as f:
+            n = struct.unpack("<Q", f.read(8))[0]
+            for name, ent in json.loads(f.read(n)).items():
+                if name != "__metadata__":
+                    shapes[name] = list(ent["shape"])
+    return shapes
+
+
 def from_pretrained(ctx, model_dir, quantizer=None, max_seq_len=1024, max_batch=1, tp_rank=0, tp_world=1, gpt=None):
     """the reference's `--hf <dir>` path (MODEL_CARD::InitHugFace, src/Utils/CLI_params.cpp:2224-2300 + Fish::LoadFolderOfST): an HF checkpoint
     directory (config.json, *.safetensors, tokenizer.json) -> (Model with every tensor loaded, Tokenizer).  `quantizer`: a Koifish "quantizer"
@@ -776,6 +791,9 @@ def from_pretrained(ctx, model_dir, quantizer=None, max_seq_len=1024, max_batch=
     import os
     with open(os.path.join(str(model_dir), "config.json")) as f:
         hf = json.load(f)
+    if "architecture" in hf and "tensor_shapes" not in hf:
+        # registry architectures may take sizes that their config does not carry from the checkpoint's tensor shapes
+        hf = dict(hf, tensor_shapes=_safetensors_shapes(str(model_dir)))
     cfg = {"hf_config": hf, "gpt": {"max_seq_len": int(max_seq_len), "max_batch": int(max_batch)}}
     cfg["gpt"].update(gpt or {})  # e.g. max_prefill, logit_rows, compute_dtype
     if quantizer:

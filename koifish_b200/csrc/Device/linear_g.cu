@@ -25,8 +25,14 @@ struct LinArgs {
     const int32_t* src_row;      // slot -> row of x; nullptr: slot
     const int32_t* slot_group;   // GEMV form: slot -> expert; nullptr: 0
     int M, N, K, ldx, ldy;
-    int out_act;                 // DUAL only: 0 = float out, 1 = bf16 out, (float activations: float out)
+    int out_act;                 // DUAL or act != 0: 0 = float out, 1 = bf16 out, (float activations: float out)
+    int act;                     // single-weight form: 0 = none, 1 = gelu (tanh form), 2 = relu squared, applied to the result
 };
+__device__ __forceinline__ float lin_act(float v, int act) {
+    if (act == 1) return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    if (act == 2) return v > 0.f ? v * v : 0.f;
+    return v;
+}
 
 template <typename TA>
 __device__ __forceinline__ float ld_act(const TA* p);
@@ -85,8 +91,8 @@ __global__ void __launch_bounds__(256) kf_lin_gemv_kernel(LinArgs a) {
     s0 = warp_sum(s0);
     if (DUAL) s1 = warp_sum(s1);
     if (lane == 0) {
-        const float r = DUAL ? silu_f(s0) * s1 : s0;
-        if (DUAL && a.out_act == 1)
+        const float r = DUAL ? silu_f(s0) * s1 : lin_act(s0, a.act);
+        if ((DUAL || a.act) && a.out_act == 1)
             ((uint16_t*)a.y)[(size_t)slot * a.ldy + n] = f32_to_bf16_bits(r);
         else
             ((float*)a.y)[(size_t)slot * a.ldy + n] = r;
@@ -238,8 +244,8 @@ __global__ void __launch_bounds__(256) kf_lin_tile_kernel(LinArgs a) {
     auto store = [&](int r, int n, float v0, float v1) {
         const int s = m0 + r;
         if (s >= hi || n >= a.N) return;
-        const float v = DUAL ? silu_f(v0) * v1 : v0;
-        if (DUAL && a.out_act == 1)
+        const float v = DUAL ? silu_f(v0) * v1 : lin_act(v0, a.act);
+        if ((DUAL || a.act) && a.out_act == 1)
             ((uint16_t*)a.y)[(size_t)s * a.ldy + n] = f32_to_bf16_bits(v);
         else
             ((float*)a.y)[(size_t)s * a.ldy + n] = v;
@@ -319,4 +325,16 @@ extern "C" int kf_linear_grouped(kf_ctx* ctx, void* y, int ldy, const void* cons
     a.Wt0 = (const uint16_t* const*)w_table, a.Wt1 = (const uint16_t* const*)w2_table, a.x = x, a.y = y, a.M = slots, a.N = N, a.K = K;
     a.ldx = ldx, a.ldy = ldy, a.offsets = offsets, a.slot_group = slot_group, a.src_row = src_row, a.out_act = act_f32 ? 0 : 1;
     return dispatch(ctx, a, slots, n_groups, slots <= kGemvMaxSlots, w2_table != nullptr, act_f32);
+}
+
+// The single-weight grouped form with an activation on the result (1: gelu, tanh form; 2: relu squared), written in the activation type
+// (bf16 bits, or float when act_f32): the up projection of experts that have no gate.  act 0 = kf_linear_grouped without a second table.
+extern "C" int kf_linear_grouped_act(kf_ctx* ctx, void* y, int ldy, const void* const* w_table, int n_groups, int N, int K, const void* x, int act_f32, int ldx,
+                                     const int32_t* offsets, const int32_t* slot_group, const int32_t* src_row, int slots, int act) {
+    if (!ctx || !y || !w_table || !x || !offsets || !slot_group) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, n_groups >= 1 && N >= 1 && K >= 1 && slots >= 1 && ldx >= K && ldy >= N && act >= 0 && act <= 2, "shape / act");
+    LinArgs a = {};
+    a.Wt0 = (const uint16_t* const*)w_table, a.x = x, a.y = y, a.M = slots, a.N = N, a.K = K;
+    a.ldx = ldx, a.ldy = ldy, a.offsets = offsets, a.slot_group = slot_group, a.src_row = src_row, a.out_act = act_f32 ? 0 : 1, a.act = act;
+    return dispatch(ctx, a, slots, n_groups, slots <= kGemvMaxSlots, false, act_f32);
 }

@@ -1,0 +1,271 @@
+// linrec.cu -- linear-recurrence sequence mixers beside the selective scan of seqmix.cu:
+//   (1) matrix-state recurrences with a decay per key channel: per head an fp32 state S [dk x dv] and, per token,
+//           S <- diag(g_t) S ;  then either   S <- S + k_t v_t^T                                   (gated linear attention)
+//                                     or      u = beta_t (v_t - S^T k_t),  S <- S + k_t u^T        (gated delta rule)
+//       and the read-out o_t = S^T q_t, which sees the token's own write.  The decay is formed in fp32 from a logit z while the
+//       token is staged: g = sigmoid(z + b)^(1/tau), or g = exp(-exp(A_h) softplus(z + b)).  q and k may be made unit vectors per head.
+//   (2) a real-gated linear recurrent unit over channels: block-diagonal gate matmuls r, i = sigmoid(W u_b + b), decay
+//       a = exp(-c r softplus(lam)), state s <- a s + sqrt(1 - a^2) i u, output s * y.
+// State lives in fp32 per (sequence slot, layer) and persists between calls; a slot whose first staged token has position 0 starts
+// from zero without a clearing pass.  Tokens are nseq sequences of T consecutive tokens (prefill panel 1 x M, batched decode M x 1).
+// No reference equivalent (the reference's inference path is the Qwen3 attention block only).
+#include <math.h>
+
+#include <algorithm>
+
+#include "kf_common.cuh"
+
+namespace {
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float log_sigmoid_f(float z) { return z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z)); }
+__device__ __forceinline__ float gelu_tanh_f(float z) { return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+
+struct ScanArgs {
+    float* y;          // [M][ldy] heads x dv
+    int ldy;
+    const float *q, *k, *v, *z, *beta;  // fp32 rows; q / k: kv-head major [G][dk]; v: [H][dv]; z: [H][dk]; beta logits [H] (delta only)
+    int ldq, ldk, ldv, ldz, ldb;
+    const uint16_t* zbias;   // bf16 [H * dk]
+    const uint16_t* A_log;   // bf16 [H] (decay kind 1)
+    float* state;            // [slot][H][dv][dk]
+    size_t state_stride;
+    const int32_t *pos, *slot;
+    int T, H, G, dk, dv;
+    int R, PB, TB;
+    int delta;               // 1: delta-rule write, 0: plain outer-product write
+    int decay_kind;          // 0: sigmoid(z + b)^(1/tau) ; 1: exp(-exp(A_h) softplus(z + b))
+    int unit_qk;             // q, k divided by sqrt(sum x^2 + unit_eps) per head
+    float inv_tau, q_scale, unit_eps;
+};
+
+// grid (heads, sequences, column chunks).  Thread (pl, r) keeps rows n = i * R + r (i < NPT) of state column p0 + pl in registers; the R
+// lanes of a column are adjacent and reduce with shuffles.  TB tokens are staged in shared memory per pass: k, q (normalised there),
+// the decay (formed there), v, beta.
+constexpr int NPT = 16;
+__global__ void __launch_bounds__(1024) kf_gated_scan_kernel(ScanArgs a) {
+    extern __shared__ float sm[];
+    const int dk = a.dk, TB = a.TB, PB = a.PB, R = a.R;
+    float* sK = sm;                  // [TB][dk]
+    float* sQ = sK + TB * dk;        // [TB][dk]
+    float* sG = sQ + TB * dk;        // [TB][dk]
+    float* sV = sG + TB * dk;        // [TB][PB]
+    float* sB = sV + TB * PB;        // [TB]
+    const int h = blockIdx.x, seq = blockIdx.y, p0 = blockIdx.z * PB;
+    const int kh = h / (a.H / a.G);
+    const int tid = threadIdx.x, pl = tid / R, r = tid - pl * R, p = p0 + pl;
+    const bool live = pl < PB && p < a.dv;
+    const int m0 = seq * a.T;
+    float* st = a.state + (size_t)a.slot[m0] * a.state_stride + ((size_t)h * a.dv + (live ? p : 0)) * dk;
+    const bool fresh = a.pos[m0] == 0;
+    float S[NPT];
+#pragma unroll
+    for (int i = 0; i < NPT; i++) {
+        const int n = i * R + r;
+        S[i] = (live && n < dk && !fresh) ? st[n] : 0.f;
+    }
+    const float Aexp = a.decay_kind == 1 ? expf(bf16_bits_to_f32(a.A_log[h])) : 0.f;
+    const int warp = tid >> 5, lane = tid & 31, nwarp = blockDim.x >> 5;
+    for (int t0 = 0; t0 < a.T; t0 += TB) {
+        const int nt = min(TB, a.T - t0);
+        __syncthreads();
+        for (int i = tid; i < nt * dk; i += blockDim.x) {
+            const int tt = i / dk, n = i - tt * dk;
+            const size_t m = (size_t)(m0 + t0 + tt);
+            sK[i] = a.k[m * a.ldk + kh * dk + n];
+            sQ[i] = a.q[m * a.ldq + kh * dk + n];
+            const float zz = a.z[m * a.ldz + h * dk + n] + (a.zbias ? bf16_bits_to_f32(a.zbias[h * dk + n]) : 0.f);
+            sG[i] = a.decay_kind == 1 ? expf(-Aexp * softplus_f(zz)) : expf(log_sigmoid_f(zz) * a.inv_tau);
+        }
+        for (int i = tid; i < nt * PB; i += blockDim.x) {
+            const int tt = i / PB, c = i - tt * PB;
+            sV[i] = (p0 + c < a.dv) ? a.v[(size_t)(m0 + t0 + tt) * a.ldv + h * a.dv + p0 + c] : 0.f;
+        }
+        if (a.delta)
+            for (int i = tid; i < nt; i += blockDim.x) sB[i] = sigmoid_f(a.beta[(size_t)(m0 + t0 + i) * a.ldb + h]);
+        __syncthreads();
+        // unit vectors / query scale: one warp per staged token
+        for (int tt = warp; tt < nt; tt += nwarp) {
+            float sq = 0.f, sk = 0.f;
+            if (a.unit_qk) {
+                for (int n = lane; n < dk; n += 32) sq = fmaf(sQ[tt * dk + n], sQ[tt * dk + n], sq), sk = fmaf(sK[tt * dk + n], sK[tt * dk + n], sk);
+                sq = warp_sum(sq), sk = warp_sum(sk);
+            }
+            const float fq = a.unit_qk ? a.q_scale / sqrtf(sq + a.unit_eps) : a.q_scale;
+            const float fk = a.unit_qk ? 1.f / sqrtf(sk + a.unit_eps) : 1.f;
+            for (int n = lane; n < dk; n += 32) {
+                sQ[tt * dk + n] *= fq;
+                if (a.unit_qk) sK[tt * dk + n] *= fk;
+            }
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; tt++) {
+            const float* kk = sK + tt * dk;
+            const float* qq = sQ + tt * dk;
+            const float* gg = sG + tt * dk;
+            const float vv = sV[tt * PB + (pl < PB ? pl : 0)];
+            float w = vv;
+            if (a.delta) {
+                float dot = 0.f;
+#pragma unroll
+                for (int i = 0; i < NPT; i++) {
+                    const int n = i * R + r;
+                    if (n < dk) {
+                        S[i] *= gg[n];
+                        dot = fmaf(S[i], kk[n], dot);
+                    }
+                }
+                for (int o = R >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                w = sB[tt] * (vv - dot);
+            }
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < NPT; i++) {
+                const int n = i * R + r;
+                if (n < dk) {
+                    S[i] = a.delta ? fmaf(kk[n], w, S[i]) : fmaf(gg[n], S[i], kk[n] * w);
+                    acc  = fmaf(S[i], qq[n], acc);
+                }
+            }
+            for (int o = R >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (live && r == 0) a.y[(size_t)(m0 + t0 + tt) * a.ldy + h * a.dv + p] = acc;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < NPT; i++) {
+            const int n = i * R + r;
+            if (n < dk) st[n] = S[i];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------ real-gated LRU
+// Gates of TT tokens x 128 output channels of one block b:  r = sigmoid(Wr[b] u_b + br), i = sigmoid(Wi[b] u_b + bi), fp32 FMAs over
+// the bf16 weights (staged transposed through shared memory so that every weight is read once per TT tokens); then
+//   a = exp(-c r softplus(lam)),  A[m][ch] = a,  Bv[m][ch] = sqrt(1 - a^2) i u.
+constexpr int GT = 8;
+__global__ void __launch_bounds__(128) kf_rglru_gates_kernel(float* __restrict__ A, float* __restrict__ Bv, const float* __restrict__ u, int ldu,
+                                                             const uint16_t* __restrict__ Wr, const uint16_t* __restrict__ br, const uint16_t* __restrict__ Wi,
+                                                             const uint16_t* __restrict__ bi, const uint16_t* __restrict__ lam, int M, int width, int bs,
+                                                             float c) {
+    __shared__ float su[GT][32];
+    __shared__ float swr[32][129], swi[32][129];
+    const int m0 = blockIdx.x * GT, b = blockIdx.y, o0 = blockIdx.z * 128, o = o0 + threadIdx.x;
+    const int nt = min(GT, M - m0);
+    const uint16_t* wr = Wr + (size_t)b * bs * bs;
+    const uint16_t* wi = Wi + (size_t)b * bs * bs;
+    float ar[GT], ai[GT];
+#pragma unroll
+    for (int t = 0; t < GT; t++) ar[t] = ai[t] = 0.f;
+    for (int i0 = 0; i0 < bs; i0 += 32) {
+        __syncthreads();
+        for (int e = threadIdx.x; e < 128 * 32; e += 128) {
+            const int oo = e >> 5, ii = e & 31;
+            const bool ok = o0 + oo < bs && i0 + ii < bs;
+            swr[ii][oo] = ok ? bf16_bits_to_f32(wr[(size_t)(o0 + oo) * bs + i0 + ii]) : 0.f;
+            swi[ii][oo] = ok ? bf16_bits_to_f32(wi[(size_t)(o0 + oo) * bs + i0 + ii]) : 0.f;
+        }
+        for (int e = threadIdx.x; e < GT * 32; e += 128) {
+            const int t = e >> 5, ii = e & 31;
+            su[t][ii] = (t < nt && i0 + ii < bs) ? u[(size_t)(m0 + t) * ldu + b * bs + i0 + ii] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int ii = 0; ii < 32; ii++) {
+            const float w1 = swr[ii][threadIdx.x], w2 = swi[ii][threadIdx.x];
+#pragma unroll
+            for (int t = 0; t < GT; t++) ar[t] = fmaf(w1, su[t][ii], ar[t]), ai[t] = fmaf(w2, su[t][ii], ai[t]);
+        }
+    }
+    if (o >= bs) return;
+    const int ch = b * bs + o;
+    const float sp = softplus_f(bf16_bits_to_f32(lam[ch])), b1 = bf16_bits_to_f32(br[ch]), b2 = bf16_bits_to_f32(bi[ch]);
+#pragma unroll
+    for (int t = 0; t < GT; t++) {
+        if (t >= nt) break;
+        const float rg = sigmoid_f(ar[t] + b1), ig = sigmoid_f(ai[t] + b2);
+        const float la = -c * rg * sp;
+        const size_t m = (size_t)(m0 + t);
+        A[m * width + ch]  = expf(la);
+        Bv[m * width + ch] = sqrtf(-expm1f(2.f * la)) * ig * u[m * ldu + ch];
+    }
+}
+// one thread per (sequence, channel): s <- A s + Bv along the T tokens; out = s * gelu_tanh(y + yb) in the activation type
+template <typename TO>
+__global__ void kf_rglru_scan_kernel(TO* __restrict__ out, int ldo, const float* __restrict__ A, const float* __restrict__ Bv, const float* __restrict__ y,
+                                     int ldy, const uint16_t* __restrict__ yb, float* __restrict__ state, size_t state_stride,
+                                     const int32_t* __restrict__ pos, const int32_t* __restrict__ slot, int T, int width) {
+    const int seq = blockIdx.y, ch = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ch >= width) return;
+    const int m0 = seq * T;
+    float* st = state + (size_t)slot[m0] * state_stride + ch;
+    float s = pos[m0] == 0 ? 0.f : *st;
+    const float bias = yb ? bf16_bits_to_f32(yb[ch]) : 0.f;
+    for (int t = 0; t < T; t++) {
+        const size_t m = (size_t)(m0 + t);
+        s = fmaf(A[m * width + ch], s, Bv[m * width + ch]);
+        const float o = s * gelu_tanh_f(y[m * ldy + ch] + bias);
+        if (sizeof(TO) == 2) ((uint16_t*)out)[m * ldo + ch] = f32_to_bf16_bits(o);
+        else ((float*)out)[m * ldo + ch] = o;
+    }
+    *st = s;
+}
+}  // namespace
+
+// Matrix-state recurrence over nseq x T tokens (see the head of this file).  q, k: float rows with G kv heads of dk entries at row strides
+// ldq / ldk; v: H heads of dv entries; z: decay logits H x dk (+ bf16 bias zbias or NULL); beta_logit: H per token (delta rule only).
+// decay_kind 0: g = sigmoid(z + b)^(1/tau); 1: g = exp(-exp(A_log[h]) softplus(z + b)).  state: float [slot][H][dv][dk].
+extern "C" int kf_gated_scan(kf_ctx* ctx, float* y, int ldy, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* z,
+                             int ldz, const void* zbias_bf16, const void* A_log_bf16, const float* beta_logit, int ldb, float* state, size_t state_stride,
+                             const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int H, int G, int dk, int dv, int delta, int decay_kind,
+                             float tau, int unit_qk, float unit_eps, float q_scale) {
+    if (!ctx || !y || !q || !k || !v || !z || !state || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, nseq >= 1 && T >= 1 && H >= 1 && G >= 1 && H % G == 0 && dk >= 1 && dv >= 1 && dk <= 32 * NPT, "key size <= 512, kv heads divide heads");
+    KF_REQUIRE(ctx, (!delta || beta_logit) && (decay_kind == 0 ? tau > 0.f : A_log_bf16 != nullptr) && state_stride >= (size_t)H * dk * dv, "arguments");
+    ScanArgs a = {};
+    a.y = y, a.ldy = ldy, a.q = q, a.k = k, a.v = v, a.z = z, a.beta = beta_logit, a.ldq = ldq, a.ldk = ldk, a.ldv = ldv, a.ldz = ldz, a.ldb = ldb;
+    a.zbias = (const uint16_t*)zbias_bf16, a.A_log = (const uint16_t*)A_log_bf16, a.state = state, a.state_stride = state_stride;
+    a.pos = pos_dev, a.slot = slot_dev, a.T = T, a.H = H, a.G = G, a.dk = dk, a.dv = dv, a.delta = delta, a.decay_kind = decay_kind;
+    a.unit_qk = unit_qk, a.inv_tau = decay_kind == 0 ? 1.f / tau : 0.f, a.q_scale = q_scale, a.unit_eps = unit_eps;
+    int R = 1;
+    while (R * NPT < dk) R <<= 1;
+    int PB = std::min(dv, 256 / R);  // at most 256 threads: the per-token chain is latency-bound, more CTAs hide it better than wider ones
+    while (PB > 8 && (long long)H * nseq * ((dv + PB - 1) / PB) < 2 * ctx->sm_count) PB = (PB + 1) / 2;
+    const int threads = std::max(32, ((PB * R + 31) / 32) * 32);
+    int TB = (int)std::min<size_t>(32, (44 * 1024 / sizeof(float)) / (size_t)(3 * dk + PB + 1));
+    TB = std::max(1, std::min(TB, T));
+    const size_t smem = (size_t)(3 * TB * dk + TB * PB + TB) * sizeof(float);
+    KF_REQUIRE(ctx, smem <= 48 * 1024, "staging area");
+    a.R = R, a.PB = PB, a.TB = TB;
+    kf_gated_scan_kernel<<<dim3(H, nseq, (dv + PB - 1) / PB), threads, smem, ctx->stream>>>(a);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+
+// Real-gated linear recurrent unit over `width` channels in `blocks` equal parts.  u: float [M][ldu] (the convolved branch); gate weights
+// bf16 [blocks][bs][bs] ([out][in]) with biases [width]; lam bf16 [width]; y_logit: float [M][ldy] (+ bf16 bias), the other branch before
+// its gelu.  out [M][ldo] = s * gelu_tanh(y) in the activation type.  work: float scratch [2][M][width].  state: float [slot][width].
+extern "C" int kf_rglru(kf_ctx* ctx, void* out, int out_f32, int ldo, float* work, const float* u, int ldu, const void* w_r_bf16, const void* b_r_bf16,
+                        const void* w_i_bf16, const void* b_i_bf16, const void* lam_bf16, float decay_c, const float* y_logit, int ldy,
+                        const void* y_bias_bf16, float* state, size_t state_stride, const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T,
+                        int width, int blocks) {
+    if (!ctx || !out || !work || !u || !w_r_bf16 || !b_r_bf16 || !w_i_bf16 || !b_i_bf16 || !lam_bf16 || !y_logit || !state || !pos_dev || !slot_dev)
+        return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, nseq >= 1 && T >= 1 && width >= 1 && blocks >= 1 && width % blocks == 0 && state_stride >= (size_t)width, "blocks must divide width");
+    const int M = nseq * T, bs = width / blocks;
+    float *A = work, *Bv = work + (size_t)M * width;
+    kf_rglru_gates_kernel<<<dim3((M + GT - 1) / GT, blocks, (bs + 127) / 128), 128, 0, ctx->stream>>>(
+        A, Bv, u, ldu, (const uint16_t*)w_r_bf16, (const uint16_t*)b_r_bf16, (const uint16_t*)w_i_bf16, (const uint16_t*)b_i_bf16, (const uint16_t*)lam_bf16, M,
+        width, bs, decay_c);
+    KF_LAUNCH_CHECK(ctx);
+    dim3 grid((width + 127) / 128, nseq);
+    if (out_f32)
+        kf_rglru_scan_kernel<float><<<grid, 128, 0, ctx->stream>>>((float*)out, ldo, A, Bv, y_logit, ldy, (const uint16_t*)y_bias_bf16, state, state_stride, pos_dev,
+                                                                 slot_dev, T, width);
+    else
+        kf_rglru_scan_kernel<uint16_t><<<grid, 128, 0, ctx->stream>>>((uint16_t*)out, ldo, A, Bv, y_logit, ldy, (const uint16_t*)y_bias_bf16, state, state_stride,
+                                                                    pos_dev, slot_dev, T, width);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}

@@ -5,24 +5,75 @@
 // it has no expert routing on the inference path).
 #include <math.h>
 
+#include <algorithm>
+
 #include "kf_common.cuh"
 
 namespace {
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 
-__global__ void kf_embed_f32_kernel(float* __restrict__ out, const uint16_t* __restrict__ table, const int32_t* __restrict__ tokens, int dim) {
+__device__ __forceinline__ float gelu_tanh_f(float z) { return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+
+__global__ void kf_embed_f32_kernel(float* __restrict__ out, float* __restrict__ out2, const uint16_t* __restrict__ table, const int32_t* __restrict__ tokens,
+                                    int dim, float scale) {
     const uint16_t* row = table + (size_t)tokens[blockIdx.x] * dim;
     float* o            = out + (size_t)blockIdx.x * dim;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = bf16_bits_to_f32(row[i]);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = bf16_bits_to_f32(row[i]) * scale;
+        o[i] = v;
+        if (out2) out2[(size_t)blockIdx.x * dim + i] = v;
+    }
+}
+
+// out[r][c] = act(in[r][c] + bias[c]) (* mul[r][c]) ; ACT 0: identity, 1: gelu (tanh form), 2: relu squared, 3: silu.
+// OUT 0: bf16 bits, 1: float, 2: out (float) += result.
+template <int ACT, int OUT>
+__global__ void kf_bias_act_kernel(void* __restrict__ out, int ldo, const float* __restrict__ in, int ldi, const uint16_t* __restrict__ bias,
+                                   const float* __restrict__ mul, int ldm, int cols) {
+    const int r = blockIdx.y;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < cols; c += gridDim.x * blockDim.x) {
+        float v = in[(size_t)r * ldi + c] + (bias ? bf16_bits_to_f32(bias[c]) : 0.f);
+        if (ACT == 1) v = gelu_tanh_f(v);
+        if (ACT == 2) v = v > 0.f ? v * v : 0.f;
+        if (ACT == 3) v = v * sigmoid_f(v);
+        if (mul) v *= mul[(size_t)r * ldm + c];
+        if (OUT == 0) ((uint16_t*)out)[(size_t)r * ldo + c] = f32_to_bf16_bits(v);
+        else if (OUT == 1) ((float*)out)[(size_t)r * ldo + c] = v;
+        else ((float*)out)[(size_t)r * ldo + c] += v;
+    }
+}
+// out[r][c] = gelu_tanh(in[r][c]) * table[token[r]][c0 + c]   (a per-token embedding slice gating a projection), activation type out
+template <typename TO>
+__global__ void kf_token_gate_kernel(TO* __restrict__ out, int ldo, const float* __restrict__ in, int ldi, const uint16_t* __restrict__ table, int ldt, int c0,
+                                     const int32_t* __restrict__ tokens, int cols) {
+    const int r = blockIdx.x;
+    const uint16_t* e = table + (size_t)tokens[r] * ldt + c0;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float v = gelu_tanh_f(in[(size_t)r * ldi + c]) * bf16_bits_to_f32(e[c]);
+        if (sizeof(TO) == 2) ((uint16_t*)out)[(size_t)r * ldo + c] = f32_to_bf16_bits(v);
+        else ((float*)out)[(size_t)r * ldo + c] = v;
+    }
+}
+// Weighted sum over the depth of a stack: hist[n_prev] = x (this layer's result) ; x = sum_{j < n_prev} w[j] * hist[j] + w[n_prev] * x.
+// hist: [n_prev + 1][hist_stride] floats; n = rows * dim elements.
+__global__ void kf_depth_mix_kernel(float* __restrict__ x, float* __restrict__ hist, size_t hist_stride, const uint16_t* __restrict__ w, int n_prev, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float cur = x[i];
+    hist[(size_t)n_prev * hist_stride + i] = cur;
+    float s = 0.f;
+    for (int j = 0; j < n_prev; j++) s = fmaf(bf16_bits_to_f32(w[j]), hist[(size_t)j * hist_stride + i], s);
+    x[i] = fmaf(bf16_bits_to_f32(w[n_prev]), cur, s);
 }
 
 // One block per (row, group).  v = x * gatefn(g) (GATE 0: none, 1: sigmoid(g + gate_bias), 2: silu(g));  r = v / sqrt(mean_group(v^2) + eps) * w;
+// GATE 3 / 4: the gate multiplies the normed result instead, r *= sigmoid(g) / silu(g).  w_shared: one weight of group size for all groups.
 // ACC: res[row] += mult * r (fp32 residual stream)  else  out[row] = r in the activation type.
 template <int GATE, bool ACC, typename TO>
 __global__ void __launch_bounds__(256) kf_group_norm_kernel(TO* __restrict__ out, int ldo, float* __restrict__ res, const float* __restrict__ x, int ldx,
                                                             const float* __restrict__ gate, int ldg, const uint16_t* __restrict__ gate_bias,
                                                             const uint16_t* __restrict__ w, const int32_t* __restrict__ row_idx, int dim, int groups,
-                                                            float eps, float mult) {
+                                                            float eps, float mult, int w_shared) {
     __shared__ float red[32];
     const int r = blockIdx.x, grp = blockIdx.y, gs = dim / groups;
     const int src = row_idx ? row_idx[r] : r;
@@ -45,7 +96,12 @@ __global__ void __launch_bounds__(256) kf_group_norm_kernel(TO* __restrict__ out
     ss = block_sum(ss, red);
     const float s = 1.0f / sqrtf(ss / (float)gs + eps);
     for (int i = threadIdx.x; i < gs; i += blockDim.x) {
-        const float o = val(i) * s * bf16_bits_to_f32(w[grp * gs + i]);
+        float o = val(i) * s * bf16_bits_to_f32(w[w_shared ? i : grp * gs + i]);
+        if (GATE == 3) o *= sigmoid_f(gr[i]);
+        if (GATE == 4) {
+            const float z = gr[i];
+            o *= z * sigmoid_f(z);
+        }
         if (ACC) {
             float* p = res + (size_t)r * dim + grp * gs + i;
             *p       = *p + mult * o;
@@ -64,9 +120,9 @@ __global__ void kf_f32_to_bf16_kernel(uint16_t* __restrict__ out, const float* _
 
 // ---- mixture of experts ---------------------------------------------------------------------------------------------------
 // one warp per token: `top` rounds of arg-max over the E router logits (+ bias), ties to the lower index; weights = softmax over the
-// chosen logits only.  All in fp32.
+// chosen logits only, or (full) the chosen entries of the softmax over ALL experts, not renormalised.  All in fp32.
 __global__ void __launch_bounds__(128) kf_moe_route_kernel(int32_t* __restrict__ idx, float* __restrict__ wgt, const float* __restrict__ logits, int ldl,
-                                                           const uint16_t* __restrict__ bias, int M, int E, int top) {
+                                                           const uint16_t* __restrict__ bias, int M, int E, int top, int full) {
     const int m = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (m >= M) return;
     const float* lg = logits + (size_t)m * ldl;
@@ -93,6 +149,11 @@ __global__ void __launch_bounds__(128) kf_moe_route_kernel(int32_t* __restrict__
         if (lane == 0) idx[(size_t)m * top + j] = bi, wgt[(size_t)m * top + j] = p;
         __syncwarp();
     }
+    if (full) {  // the denominator runs over every expert (first = the largest logit)
+        float d = 0.f;
+        for (int e = lane; e < E; e += 32) d += expf(lg[e] + (bias ? bf16_bits_to_f32(bias[e]) : 0.f) - first);
+        den = warp_sum(d);
+    }
     if (lane < top) {
         for (int j = lane; j < top; j += 32) wgt[(size_t)m * top + j] /= den;
     }
@@ -103,7 +164,7 @@ constexpr int kRouteSmall = 256;
 __global__ void __launch_bounds__(256) kf_moe_route_small_kernel(int32_t* __restrict__ idx, float* __restrict__ wgt, int32_t* __restrict__ offsets,
                                                                  int32_t* __restrict__ entry_slot, int32_t* __restrict__ slot_row,
                                                                  int32_t* __restrict__ slot_group, const float* __restrict__ logits, int ldl,
-                                                                 const uint16_t* __restrict__ bias, int M, int E, int top) {
+                                                                 const uint16_t* __restrict__ bias, int M, int E, int top, int full) {
     __shared__ int sidx[kRouteSmall];
     __shared__ int srank[kRouteSmall];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = M * top;
@@ -131,6 +192,11 @@ __global__ void __launch_bounds__(256) kf_moe_route_small_kernel(int32_t* __rest
             den += p;
             if (lane == 0) sidx[m * top + j] = bi, idx[(size_t)m * top + j] = bi, wgt[(size_t)m * top + j] = p;
             __syncwarp();
+        }
+        if (full) {
+            float d = 0.f;
+            for (int e = lane; e < E; e += 32) d += expf(lg[e] + (bias ? bf16_bits_to_f32(bias[e]) : 0.f) - first);
+            den = warp_sum(d);
         }
         for (int j = lane; j < top; j += 32) wgt[(size_t)m * top + j] /= den;
     }
@@ -210,42 +276,94 @@ __global__ void kf_moe_combine_kernel(float* __restrict__ out, const float* __re
 }
 }  // namespace
 
-extern "C" int kf_embed_f32(kf_ctx* ctx, float* out, const kf_tensor_desc* w, const int32_t* tokens_dev, int M) {
+// out[m] = scale * W[token[m]] as floats; out2 (optional) receives a second copy
+extern "C" int kf_embed_f32_scaled(kf_ctx* ctx, float* out, float* out2, const kf_tensor_desc* w, const int32_t* tokens_dev, int M, float scale) {
     if (!ctx || !out || !w || !tokens_dev) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, w->type == KF_T_BF16 && M >= 1, "bf16 table");
-    kf_embed_f32_kernel<<<M, 256, 0, ctx->stream>>>(out, (const uint16_t*)w->data_dev, tokens_dev, w->cols);
+    kf_embed_f32_kernel<<<M, 256, 0, ctx->stream>>>(out, out2, (const uint16_t*)w->data_dev, tokens_dev, w->cols, scale);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+extern "C" int kf_embed_f32(kf_ctx* ctx, float* out, const kf_tensor_desc* w, const int32_t* tokens_dev, int M) {
+    return kf_embed_f32_scaled(ctx, out, nullptr, w, tokens_dev, M, 1.f);
+}
+// out[rows][ldo] = act(in[rows][ldi] + bias) (* mul); act 0: none, 1: gelu (tanh form), 2: relu squared, 3: silu; out_kind 0: bf16 bits,
+// 1: float, 2: float out += result.  bias: bf16 [cols] or NULL; mul: float [rows][ldm] or NULL.
+extern "C" int kf_bias_act(kf_ctx* ctx, void* out, int out_kind, int ldo, const float* in, int ldi, const void* bias_bf16, int act, const float* mul, int ldm,
+                           int rows, int cols) {
+    if (!ctx || !out || !in) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, rows >= 1 && cols >= 1 && act >= 0 && act <= 3 && out_kind >= 0 && out_kind <= 2, "act / out kind");
+    dim3 grid(std::min(64, (cols + 255) / 256), rows);
+    const uint16_t* b = (const uint16_t*)bias_bf16;
+#define KF_BA(A, O) kf_bias_act_kernel<A, O><<<grid, 256, 0, ctx->stream>>>(out, ldo, in, ldi, b, mul, ldm, cols)
+#define KF_BA_O(A) (out_kind == 0 ? KF_BA(A, 0) : out_kind == 1 ? KF_BA(A, 1) : KF_BA(A, 2))
+    if (act == 0) KF_BA_O(0);
+    else if (act == 1) KF_BA_O(1);
+    else if (act == 2) KF_BA_O(2);
+    else KF_BA_O(3);
+#undef KF_BA_O
+#undef KF_BA
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+extern "C" int kf_token_gate(kf_ctx* ctx, void* out, int out_f32, int ldo, const float* in, int ldi, const void* table_bf16, int ldt, int c0,
+                             const int32_t* tokens_dev, int rows, int cols) {
+    if (!ctx || !out || !in || !table_bf16 || !tokens_dev) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, rows >= 1 && cols >= 1 && c0 >= 0 && c0 + cols <= ldt, "slice inside the table row");
+    if (out_f32) kf_token_gate_kernel<float><<<rows, 128, 0, ctx->stream>>>((float*)out, ldo, in, ldi, (const uint16_t*)table_bf16, ldt, c0, tokens_dev, cols);
+    else kf_token_gate_kernel<uint16_t><<<rows, 128, 0, ctx->stream>>>((uint16_t*)out, ldo, in, ldi, (const uint16_t*)table_bf16, ldt, c0, tokens_dev, cols);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+extern "C" int kf_depth_mix(kf_ctx* ctx, float* x, float* hist, size_t hist_stride, const void* w_bf16, int n_prev, size_t n) {
+    if (!ctx || !x || !hist || !w_bf16) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, n_prev >= 0 && n >= 1 && hist_stride >= n, "history stride");
+    kf_depth_mix_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(x, hist, hist_stride, (const uint16_t*)w_bf16, n_prev, n);
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;
 }
 
 // gate_kind 0: none; 1: x * sigmoid(gate + gate_bias); 2: x * silu(gate).  out_kind 0: bf16 bits [rows][ldo]; 1: float [rows][ldo];
 // 2: res[rows][dim] += mult * result (out is ignored).  row_idx (device, optional): source row of each output row.
-extern "C" int kf_group_rmsnorm(kf_ctx* ctx, void* out, int out_kind, int ldo, float* res, float mult, const float* x, int ldx, const float* gate, int ldg,
-                                const void* gate_bias_bf16, int gate_kind, const void* w_bf16, const int32_t* row_idx, int rows, int dim, int groups,
-                                float eps) {
+// gate_kind 3 / 4: sigmoid(gate) / silu(gate) multiply the normed result; w_shared: the weight has dim / groups entries, used by every group.
+extern "C" int kf_group_rmsnorm_ex(kf_ctx* ctx, void* out, int out_kind, int ldo, float* res, float mult, const float* x, int ldx, const float* gate, int ldg,
+                                   const void* gate_bias_bf16, int gate_kind, const void* w_bf16, int w_shared, const int32_t* row_idx, int rows, int dim,
+                                   int groups, float eps) {
     if (!ctx || !x || !w_bf16) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, rows >= 1 && dim >= 1 && groups >= 1 && dim % groups == 0, "groups must divide dim");
-    KF_REQUIRE(ctx, gate_kind >= 0 && gate_kind <= 2 && (gate_kind == 0 || gate) && out_kind >= 0 && out_kind <= 2 && (out_kind == 2 ? res != nullptr : out != nullptr),
+    KF_REQUIRE(ctx, gate_kind >= 0 && gate_kind <= 4 && (gate_kind == 0 || gate) && out_kind >= 0 && out_kind <= 2 && (out_kind == 2 ? res != nullptr : out != nullptr),
                "gate / out kind");
     dim3 grid(rows, groups);
     const uint16_t *gb = (const uint16_t*)gate_bias_bf16, *w = (const uint16_t*)w_bf16;
-#define KF_GN(G, A, T) kf_group_norm_kernel<G, A, T><<<grid, 256, 0, ctx->stream>>>((T*)out, ldo, res, x, ldx, gate, ldg, gb, w, row_idx, dim, groups, eps, mult)
+#define KF_GN(G, A, T) kf_group_norm_kernel<G, A, T><<<grid, 256, 0, ctx->stream>>>((T*)out, ldo, res, x, ldx, gate, ldg, gb, w, row_idx, dim, groups, eps, mult, w_shared)
     if (out_kind == 2) {
         if (gate_kind == 0) KF_GN(0, true, float);
         else if (gate_kind == 1) KF_GN(1, true, float);
-        else KF_GN(2, true, float);
+        else if (gate_kind == 2) KF_GN(2, true, float);
+        else if (gate_kind == 3) KF_GN(3, true, float);
+        else KF_GN(4, true, float);
     } else if (out_kind == 1) {
         if (gate_kind == 0) KF_GN(0, false, float);
         else if (gate_kind == 1) KF_GN(1, false, float);
-        else KF_GN(2, false, float);
+        else if (gate_kind == 2) KF_GN(2, false, float);
+        else if (gate_kind == 3) KF_GN(3, false, float);
+        else KF_GN(4, false, float);
     } else {
         if (gate_kind == 0) KF_GN(0, false, uint16_t);
         else if (gate_kind == 1) KF_GN(1, false, uint16_t);
-        else KF_GN(2, false, uint16_t);
+        else if (gate_kind == 2) KF_GN(2, false, uint16_t);
+        else if (gate_kind == 3) KF_GN(3, false, uint16_t);
+        else KF_GN(4, false, uint16_t);
     }
 #undef KF_GN
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;
+}
+extern "C" int kf_group_rmsnorm(kf_ctx* ctx, void* out, int out_kind, int ldo, float* res, float mult, const float* x, int ldx, const float* gate, int ldg,
+                                const void* gate_bias_bf16, int gate_kind, const void* w_bf16, const int32_t* row_idx, int rows, int dim, int groups,
+                                float eps) {
+    if (gate_kind > 2) return KF_ERR_BAD_ARG;
+    return kf_group_rmsnorm_ex(ctx, out, out_kind, ldo, res, mult, x, ldx, gate, ldg, gate_bias_bf16, gate_kind, w_bf16, 0, row_idx, rows, dim, groups, eps);
 }
 extern "C" int kf_f32_to_bf16(kf_ctx* ctx, void* out_bf16, const float* in, size_t n) {
     if (!ctx || !out_bf16 || !in) return KF_ERR_BAD_ARG;
@@ -258,18 +376,19 @@ extern "C" int kf_f32_to_bf16(kf_ctx* ctx, void* out_bf16, const float* in, size
 // Router of a mixture of experts over fp32 logits [M][ldl] (+ bf16 bias [E] or NULL): idx / wgt [M][top]; then the dispatch tables:
 // offsets [E + 1], entry_slot [M * top] (where each (token, choice) sits among the expert-sorted slots), slot_row / slot_group [M * top].
 // work: device int32 scratch of 2 * M * top + E entries.
-extern "C" int kf_moe_route(kf_ctx* ctx, int32_t* idx, float* wgt, int32_t* offsets, int32_t* entry_slot, int32_t* slot_row, int32_t* slot_group,
-                            int32_t* work, const float* logits, int ldl, const void* bias_bf16, int M, int E, int top) {
+// full_softmax 0: weights = softmax over the chosen logits; 1: the chosen entries of the softmax over all E experts (not renormalised).
+extern "C" int kf_moe_route_ex(kf_ctx* ctx, int32_t* idx, float* wgt, int32_t* offsets, int32_t* entry_slot, int32_t* slot_row, int32_t* slot_group,
+                               int32_t* work, const float* logits, int ldl, const void* bias_bf16, int M, int E, int top, int full_softmax) {
     if (!ctx || !idx || !wgt || !offsets || !entry_slot || !slot_row || !slot_group || !work || !logits) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, M >= 1 && E >= 1 && top >= 1 && top <= E && ldl >= E, "1 <= top <= experts");
     const int n = M * top;
     if (n <= kRouteSmall && (long long)E * n <= 16384) {
-        kf_moe_route_small_kernel<<<1, 256, 0, ctx->stream>>>(idx, wgt, offsets, entry_slot, slot_row, slot_group, logits, ldl, (const uint16_t*)bias_bf16, M, E, top);
+        kf_moe_route_small_kernel<<<1, 256, 0, ctx->stream>>>(idx, wgt, offsets, entry_slot, slot_row, slot_group, logits, ldl, (const uint16_t*)bias_bf16, M, E, top, full_softmax);
         KF_LAUNCH_CHECK(ctx);
         return KF_OK;
     }
     int32_t *rank = work, *count = work + n;
-    kf_moe_route_kernel<<<(M + 3) / 4, 128, 0, ctx->stream>>>(idx, wgt, logits, ldl, (const uint16_t*)bias_bf16, M, E, top);
+    kf_moe_route_kernel<<<(M + 3) / 4, 128, 0, ctx->stream>>>(idx, wgt, logits, ldl, (const uint16_t*)bias_bf16, M, E, top, full_softmax);
     KF_LAUNCH_CHECK(ctx);
     kf_moe_rank_kernel<<<E, 256, 0, ctx->stream>>>(rank, count, idx, n);
     KF_LAUNCH_CHECK(ctx);
@@ -278,6 +397,10 @@ extern "C" int kf_moe_route(kf_ctx* ctx, int32_t* idx, float* wgt, int32_t* offs
     kf_moe_slots_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>(entry_slot, slot_row, slot_group, idx, rank, offsets, n, top);
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;
+}
+extern "C" int kf_moe_route(kf_ctx* ctx, int32_t* idx, float* wgt, int32_t* offsets, int32_t* entry_slot, int32_t* slot_row, int32_t* slot_group,
+                            int32_t* work, const float* logits, int ldl, const void* bias_bf16, int M, int E, int top) {
+    return kf_moe_route_ex(ctx, idx, wgt, offsets, entry_slot, slot_row, slot_group, work, logits, ldl, bias_bf16, M, E, top, 0);
 }
 extern "C" int kf_moe_combine(kf_ctx* ctx, float* out, const float* y_slots, const int32_t* entry_slot, const float* wgt, const float* shared,
                               const float* shared_gate_logit, int ld_gate, int M, int dim, int top) {

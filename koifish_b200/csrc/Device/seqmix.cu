@@ -24,7 +24,7 @@ __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log
 // the start of the sequence.  tail: [slot][K-1][C], oldest first.
 __global__ void kf_conv_silu_kernel(float* __restrict__ out, const float* __restrict__ u, int ldu, const uint16_t* __restrict__ w, const uint16_t* __restrict__ b,
                                     const float* __restrict__ tail, size_t tail_stride, const int32_t* __restrict__ pos, const int32_t* __restrict__ slot,
-                                    int T, int C, int K) {
+                                    int T, int C, int K, int act) {
     const int m = blockIdx.x, seq = m / T, t = m - seq * T;
     const int p = pos[m];
     const float* tl = tail + (size_t)slot[m] * tail_stride;
@@ -38,7 +38,7 @@ __global__ void kf_conv_silu_kernel(float* __restrict__ out, const float* __rest
             else v = tl[(size_t)(K - 1 + (t - back)) * C + c];  // t - back in [-(K-1), -1]
             s = fmaf(bf16_bits_to_f32(w[(size_t)c * K + j]), v, s);
         }
-        out[(size_t)m * C + c] = s * sigmoid_f(s);
+        out[(size_t)m * C + c] = act ? s * sigmoid_f(s) : s;
     }
 }
 // the new tail of each sequence: its last K-1 inputs (a thread owns a channel and walks oldest -> newest, so the in-place shift is safe)
@@ -517,18 +517,23 @@ __global__ void __launch_bounds__(256) kf_latent_expand_kernel(TO* __restrict__ 
 }  // namespace
 
 // xbc_out [M][C] = silu(conv(u[:, c0 : c0 + C])) per channel; then the slot's tail is advanced.  u: float [M][ldu]; w bf16 [C][K]; b bf16 [C].
-extern "C" int kf_conv_silu(kf_ctx* ctx, float* xbc_out, const float* u, int ldu, int c0, const void* w_bf16, const void* b_bf16, float* tail,
-                            size_t tail_stride, const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int C, int K) {
+// act 0: no activation, 1: SiLU.  tail may be shared by several convolutions of one layer: pass each its own region of the slot's tail.
+extern "C" int kf_conv1d(kf_ctx* ctx, float* xbc_out, const float* u, int ldu, int c0, const void* w_bf16, const void* b_bf16, float* tail,
+                         size_t tail_stride, const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int C, int K, int act) {
     if (!ctx || !xbc_out || !u || !w_bf16 || !tail || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, nseq >= 1 && T >= 1 && C >= 1 && K >= 1 && tail_stride >= (size_t)(K - 1) * C, "shape");
     kf_conv_silu_kernel<<<dim3(nseq * T, (C + 255) / 256), 256, 0, ctx->stream>>>(xbc_out, u + c0, ldu, (const uint16_t*)w_bf16, (const uint16_t*)b_bf16, tail, tail_stride, pos_dev,
-                                                           slot_dev, T, C, K);
+                                                           slot_dev, T, C, K, act);
     KF_LAUNCH_CHECK(ctx);
     if (K > 1) {
         kf_conv_tail_kernel<<<dim3(nseq, (C + 255) / 256), 256, 0, ctx->stream>>>(tail, tail_stride, u + c0, ldu, pos_dev, slot_dev, T, C, K);
         KF_LAUNCH_CHECK(ctx);
     }
     return KF_OK;
+}
+extern "C" int kf_conv_silu(kf_ctx* ctx, float* xbc_out, const float* u, int ldu, int c0, const void* w_bf16, const void* b_bf16, float* tail,
+                            size_t tail_stride, const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int C, int K) {
+    return kf_conv1d(ctx, xbc_out, u, ldu, c0, w_bf16, b_bf16, tail, tail_stride, pos_dev, slot_dev, nseq, T, C, K, 1);
 }
 // y [M][ldy] (heads x P) from xbc [M][C = H*P + 2*G*N] (x | B | C after the convolution) and the step logits u[:, dt_off + h];
 // state: float [slot][H][P][N] with state_stride floats per slot.

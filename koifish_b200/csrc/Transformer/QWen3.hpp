@@ -21,7 +21,7 @@ namespace koifish {
 // One layer of a hybrid stack (config "layers": [{"type", "mixer": {...}, "mlp": {...} | null}, ...]): which sequence mixer it has, with
 // that mixer's sizes, and its feed-forward.  Layers of one model may differ in every size.
 struct MIXER_CARD {
-    std::string type;  // "mamba2" (state-space) | "latent_attention"
+    std::string type;  // "mamba2" (state-space) | "latent_attention" | "channel_delta" | "gla" | "parallel" (attention beside a gated LRU)
     // state-space mixer: heads x vdim inner channels, state rows per head, B/C groups, gated-norm groups, convolution taps
     int heads = 0, vdim = 0, state = 0, groups = 1, norm_groups = 1, conv = 1;
     // latent attention: per head `dim` plain + `rot_dim` rotated query/key entries, values of vdim, latent rank; rotation on the first
@@ -29,9 +29,19 @@ struct MIXER_CARD {
     int dim = 0, rot_dim = 0, kv_rank = 0, rot_dims = 0;
     double rot_base = 10000.0;
     float scale = 1.f;
+    // matrix-state recurrences (gated delta rule, gated linear attention): heads x vdim values, kv_heads x dim queries / keys, decay
+    // temperature tau (gla), low ranks of the decay and gate projections (read from the tensors' shapes)
+    int kv_heads = 0, rank_a = 0, rank_g = 0;
+    float tau = 1.f;
+    // attention with a logarithmic distance penalty and a query temperature t = 1 + coef * ln(floor((pos + 1) / every) + 1) (every 0: none)
+    float qt_coef = 0.f;
+    int qt_every  = 0;
+    // real-gated linear recurrent unit beside the attention of a "parallel" mixer
+    int lru_width = 0, lru_blocks = 1, lru_conv = 1;
 };
 struct MOE_CARD {
     bool present = false;
+    bool dense   = false;  // one feed-forward of width ff with biases instead of routed experts
     int experts = 0, top = 0, ff = 0;
     int shared_ff = 0;  // 0: no shared expert
 };
@@ -62,6 +72,8 @@ struct MODEL_CARD {
     float residual_mult = 1.f;
     bool compute_f32    = false;  // gpt.compute_dtype = "float32": activations, caches and matmuls in true 32-bit (hybrid stacks only)
     int logit_rows_cfg  = 0;      // gpt.logit_rows: rows of the logits buffers (default max(64, max_batch))
+    float embed_scale   = 1.f;    // the embedding row is multiplied by this
+    int side_dim        = 0;      // per-layer token input: entries of the side embedding that each layer reads (0: none)
     bool IsHybrid() const { return !layers.empty(); }
 
     // accepts a Koifish JSON (cases/qwen3/*.json layout) or an HF config.json, optionally wrapped as {"hf_config": {...}}
@@ -173,6 +185,7 @@ struct ARCH_ENTRY {
 };
 const ARCH_ENTRY* FindArch(const std::string& name);
 const ARCH_ENTRY* SipazenArch();  // Sipazen.cpp
+const ARCH_ENTRY* KivoraxArch();  // Kivorax.cpp
 
 // ---- the model ------------------------------------------------------------------------------------------------------------
 struct Fish {

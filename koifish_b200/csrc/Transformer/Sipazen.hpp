@@ -25,6 +25,10 @@ struct HybridScratch {  // device buffers shared by all layers, sized for max_to
     void* hs = nullptr;          // shared expert hidden, activation type
     float* shared = nullptr;     // [T][E]
     void* head_in = nullptr;     // final norm of the selected rows, activation type
+    // stacks with low-rank projections, a per-layer token input, a depth-weighted residual, a gated LRU
+    void* mid = nullptr;         // second-stage matmul inputs (low-rank middles, token-gated side input), activation type
+    float* hist = nullptr;       // [layers + 1][T][E] results of the embedding and of every layer
+    float* lru_work = nullptr;   // [2][T][widest LRU]: decay and input term of every token
 };
 
 // Several weights that read the same normed input, stacked row-wise into ONE matrix at load (rows padded to a multiple of 16 so that the

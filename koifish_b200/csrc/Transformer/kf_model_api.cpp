@@ -532,8 +532,10 @@ extern "C" int kf_model_load_safetensors(kf_model* m, const char* path_or_dir, i
                     continue;
                 }
                 if (e.dtype != "BF16" && e.dtype != "F16" && e.dtype != "F32") throw std::runtime_error("'" + e.name + "': dtype " + e.dtype + " cannot be a weight");
-                if (e.shape.empty() || e.shape.size() > 2) throw std::runtime_error("'" + e.name + "': expected a vector or a matrix");
-                const int64_t rows = e.shape.size() == 2 ? e.shape[0] : 1, cols = e.shape.back();
+                if (e.shape.empty() || e.shape.size() > 3) throw std::runtime_error("'" + e.name + "': expected a vector, a matrix or a stack of matrices");
+                int64_t rows = 1;  // a stack of matrices [n][r][c] is held as [n * r][c]
+                for (size_t d = 0; d + 1 < e.shape.size(); d++) rows *= e.shape[d];
+                const int64_t cols = e.shape.back();
                 if (rows <= 0 || cols <= 0 || rows > 0x7fffffff || cols > 0x7fffffff) throw std::runtime_error("'" + e.name + "': bad shape");
                 raw.resize(e.end - e.begin);
                 if (kf_st_read(f, e, raw.data(), &err) != 0) throw std::runtime_error(err);
