@@ -1,5 +1,6 @@
-"""Prefill and decode throughput of the Sipazen hybrid stack beside a Qwen3 stack of equal width, depth and active feed-forward width,
-both bf16 with random weights (bench.py --compare-arch).  One JSON line per (model, size).
+"""Prefill and decode throughput of a hybrid stack (bench.py --compare-arch sipazen | kivorax) beside the closest existing models at equal
+width, depth and active feed-forward width: Sipazen beside Qwen3; Kivorax beside Sipazen (the other recurrence + attention + experts
+stack of this runtime) and Qwen3.  All bf16 with random weights.  One JSON line per (model, size).
 
     prefill: a prompt of --prompt tokens through the model's own step function in panels, timed with CUDA events after 3 warm-up prompts
     decode : the device-resident greedy loop (one CUDA-graph replay per token) at context --prompt, after W warm-up tokens
@@ -14,15 +15,18 @@ PRESETS = {
     "s": dict(width=1024, vocab=32768, pattern="mmamma",
               ssm=dict(heads=32, vdim=64, state=64, groups=1, norm_groups=1, conv=4),
               att=dict(heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=256),
-              moe=dict(experts=16, top=2, ff=512, shared=1024)),
+              moe=dict(experts=16, top=2, ff=512, shared=1024),
+              kvx=dict(pattern="ddgpdg", heads=8, dim=64, rank=32)),
     "m": dict(width=2048, vocab=65536, pattern="mmammama",
               ssm=dict(heads=64, vdim=64, state=128, groups=8, norm_groups=8, conv=4),
               att=dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512),
-              moe=dict(experts=64, top=6, ff=1408, shared=2816)),
+              moe=dict(experts=64, top=6, ff=1408, shared=2816),
+              kvx=dict(pattern="ddgpddgp", heads=16, dim=64, rank=64)),
     "l": dict(width=4096, vocab=65536, pattern="mmam",
               ssm=dict(heads=128, vdim=64, state=128, groups=8, norm_groups=8, conv=4),
               att=dict(heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512),
-              moe=dict(experts=32, top=4, ff=2048, shared=4096)),
+              moe=dict(experts=32, top=4, ff=2048, shared=4096),
+              kvx=dict(pattern="dgpd", heads=32, dim=64, rank=64)),
 }
 
 
@@ -40,6 +44,39 @@ def sipazen_config(p):
     return {"architecture": "Sipazen", "vocab": p["vocab"], "width": p["width"], "residual_mult": 0.7, "norm": {"eps": 1e-5, "groups": 4}, "layers": layers}
 
 
+def kivorax_config(p):
+    """layers d = gated delta rule, g = gated linear attention, p = attention beside a gated LRU; the first layer's feed-forward is dense"""
+    w, m, k = p["width"], p["moe"], p["kvx"]
+    layers = []
+    for i, ch in enumerate(k["pattern"]):
+        if ch == "d":
+            mixer, typ = dict(heads=k["heads"], kv_heads=k["heads"] // 2, dim=k["dim"], vdim=2 * k["dim"], conv=4, a_rank=k["rank"], g_rank=k["rank"]), "channel_delta"
+        elif ch == "g":
+            mixer, typ = dict(heads=k["heads"], dim=k["dim"], vdim=2 * k["dim"], tau=16.0, a_rank=k["rank"]), "gla"
+        else:
+            mixer = dict(left=dict(heads=k["heads"], kv_heads=max(1, k["heads"] // 4), dim=128, vdim=128, scale=128 ** -0.5, q_temp=dict(coef=0.5, every=256)),
+                         right=dict(width=w, blocks=k["heads"], conv=4))
+            typ = "parallel"
+        mlp = {"kind": "dense", "ff": m["top"] * m["ff"]} if i == 0 else {"kind": "moe", "router": {"experts": m["experts"], "top": m["top"]}, "expert": {"ff": m["ff"]}}
+        layers.append({"type": typ, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Kivorax", "vocab": p["vocab"], "width": w, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "token_side": {"dim": 64}, "layers": layers}
+
+
+def kivorax_fixups(model, cfg):
+    """tensors that random normal weights would make meaningless: positive distance-penalty numbers, depth weights (0, .., 0, 1), unit norms"""
+    import numpy as np
+    import torch
+
+    def bits(a):
+        return (torch.tensor(np.asarray(a, dtype=np.float32)).view(torch.int32).numpy().astype(np.uint32) >> 16).astype(np.uint16)
+    for i, ly in enumerate(cfg["layers"]):
+        model.set_tensor("l%d.dwa" % i, bits([0.0] * (i + 1) + [1.0]))
+        if ly["type"] == "parallel":
+            h = ly["mixer"]["left"]["heads"]
+            model.set_tensor("l%d.mix.left.r1" % i, bits([0.5] * h))
+            model.set_tensor("l%d.mix.left.r2" % i, bits([0.25] * h))
+
+
 def run(args, ctx, stream):
     import numpy as np
     import torch
@@ -51,15 +88,22 @@ def run(args, ctx, stream):
         p = PRESETS[size]
         n_layer = len(p["pattern"])
         ff_active = p["moe"]["top"] * p["moe"]["ff"] + p["moe"]["shared"]
-        cfgs = {
+        cfgs = {}
+        if args.compare_arch == "kivorax":
+            kcfg = kivorax_config(p)
+            cfgs["kivorax"] = {"hf_config": kcfg, "gpt": {"max_seq_len": P + args.steps + args.warmup + 64, "max_batch": 1, "max_prefill": panel},
+                               "init": {"sigma": 0.02, "norm_sigma": 0.02}}
+        cfgs.update({
             "sipazen": {"hf_config": sipazen_config(p), "gpt": {"max_seq_len": P + args.steps + args.warmup + 64, "max_batch": 1, "max_prefill": panel},
                         "init": {"sigma": 0.02, "norm_sigma": 0.02}},
             "qwen3": kf.qwen3_config(n_layer, p["width"], (ff_active + 127) // 128 * 128, p["width"] // 128, max(1, p["width"] // 512), 128, p["vocab"], None, False,
                                      P + args.steps + args.warmup + 64, 1, 42, 1e6, max_prefill=panel),
-        }
+        })
         for name, cfg in cfgs.items():
             model = kf.Model(ctx, cfg)
             model.init_random()
+            if name == "kivorax":
+                kivorax_fixups(model, kcfg)
             toks = ((np.arange(P) * 37 + 11) % p["vocab"]).astype(np.int32)
 
             def prompt():
@@ -91,7 +135,7 @@ def run(args, ctx, stream):
             torch.cuda.synchronize()
             decode_ms = e0.elapsed_time(e1) / args.steps
             info = model.info
-            line = {"bench": "arch-compare", "model": name, "size": size, "width": p["width"], "layers": n_layer, "pattern": p["pattern"],
+            line = {"bench": "arch-compare", "model": name, "size": size, "width": p["width"], "layers": n_layer, "pattern": p["kvx"]["pattern"] if name == "kivorax" else p["pattern"],
                     "weight_gb": round(info.weight_bytes / 1e9, 3), "prompt": P, "panel": panel,
                     "prefill_tok_s": round(P / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3), "prefill_launches": prefill_launches,
                     "decode_tok_s": round(1e3 / decode_ms, 1), "decode_ms": round(decode_ms, 4), "decode_launches_per_token": (ctx.launches - l0) / args.steps,

@@ -1,0 +1,300 @@
+"""GPU tests of the Kivorax stack against the plain float64 restatement in kivorax_ref.py, on small random models made here.
+
+Gates: with gpt.compute_dtype = float32 the logits agree to 2e-4 (rms of the difference, mean removed, over the rms of the logits);
+in bf16 nine rows in ten to 6e-2.  Weights are drawn on the bf16 grid, so both sides hold the same numbers.  Where random weights would
+hide a fault they are shaped: queries scaled up and distance penalties made small so that a far key wins the softmax; decays set slow
+so that the first tokens still matter hundreds of steps later; the side embedding scaled up so that a wrong slice shows.
+"""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import koifish_b200 as kf
+import kivorax_ref as ref
+from kivorax_models import bf16_grid, bits, config, delta, dense, gla, moe, pair, tokens, weights
+from st_util import write_safetensors
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOL = {True: 2e-4, False: 6e-2}
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = kf.Context(0)
+    yield c
+    c.close()
+
+
+def build(ctx, cfg, W, f32, max_seq=256, slots=2, panel=64, logit_rows=None):
+    gpt = {"max_seq_len": max_seq, "max_batch": slots, "max_prefill": panel, "logit_rows": logit_rows or panel}
+    if f32:
+        gpt["compute_dtype"] = "float32"
+    m = kf.Model(ctx, {"hf_config": cfg, "gpt": gpt})
+    assert sorted(m.tensor_names()) == sorted(W.keys())
+    for k, v in W.items():
+        m.set_tensor(k, bits(v).reshape(-1, v.shape[-1]) if v.dim() > 1 else bits(v))
+    return m
+
+
+def rel(got, want, q=1.0):
+    """largest (q = 1) or q-quantile row error: rms of the difference, mean removed, over the rms of the wanted logits"""
+    d = np.asarray(got, dtype=np.float64) - np.asarray(want, dtype=np.float64)
+    d = d - d.mean(-1, keepdims=True)
+    w = np.asarray(want, dtype=np.float64)
+    w = w - w.mean(-1, keepdims=True)
+    return float(np.quantile(np.atleast_1d(np.sqrt((d ** 2).mean(-1))), q) / np.sqrt((w ** 2).mean()))
+
+
+def close(got, want, f32):
+    """float32: every row within 2e-4.  bf16: nine rows in ten within 6e-2 and none beyond 0.5 (the bf16 rounding of a router's input may
+    move a token to another expert where two logits are close; the strict float32 run of the same case rules that out as a fault)."""
+    if f32:
+        return rel(got, want) < TOL[True]
+    return rel(got, want, 0.9) < TOL[False] and rel(got, want) < 0.5
+
+
+def oracle(cfg, W, toks):
+    return ref.forward(cfg, W, list(toks)).numpy()
+
+
+def run_cut(model, toks, cuts, slot=0):
+    """feed toks in portions of the given sizes (the rest one by one); fp32 logits of every position"""
+    out, at = [], 0
+    sizes = list(cuts)
+    while at < len(toks):
+        n = sizes.pop(0) if sizes else 1
+        n = min(n, len(toks) - at)
+        lg, _ = model.forward_rows(toks[at:at + n], at, slot=slot, rows=list(range(n)))
+        out.append(lg)
+        at += n
+    return np.concatenate(out)
+
+
+FULL = [(delta(), dense()), (gla(), moe()), (pair(), moe(experts=4, top=3, ff=16)), (delta(heads=2, kv_heads=2, dim=8, vdim=8, conv=2), None),
+        (pair(heads=2, kv_heads=1, dim=8, vdim=40, every=5, width=16, blocks=1, conv=2), dense(24))]
+
+
+# ------------------------------------------------------------------------------------------------------------ each mechanism alone
+@pytest.mark.parametrize("f32", [True, False])
+@pytest.mark.parametrize("layer", [
+    (delta(), None),
+    (delta(heads=3, kv_heads=3, dim=40, vdim=7, conv=1, a_rank=3, g_rank=9), None),       # one tap (no tail), key size over several lanes
+    (delta(heads=1, kv_heads=1, dim=8, vdim=8, conv=5, a_rank=8, g_rank=8), None),        # one head, all sizes equal
+    (gla(), None),
+    (gla(heads=1, dim=33, vdim=5, tau=1.0, a_rank=2), None),                              # tau 1: the decay is the sigmoid itself
+    (pair(), None),
+    (pair(heads=3, kv_heads=3, dim=20, vdim=70, every=0, width=10, blocks=1, conv=1), None),   # no temperature, one block, one tap, wide values
+    (pair(heads=6, kv_heads=1, dim=16, vdim=8, every=1, coef=1.5, width=32, blocks=8), None),  # temperature that moves at every token
+    (gla(heads=1, dim=8, vdim=8), dense()),
+    (gla(heads=1, dim=8, vdim=8), moe(experts=4, top=1, ff=8)),
+    (gla(heads=1, dim=8, vdim=8), moe(experts=1, top=1, ff=20)),
+    (gla(heads=1, dim=8, vdim=8), moe(experts=6, top=6, ff=12)),                          # every expert chosen: the weights sum to 1
+], ids=["delta", "delta_conv1_wide_key", "delta_one_head", "gla", "gla_tau1", "pair", "pair_plain", "pair_temp_every1", "dense", "moe_top1",
+        "moe_one_expert", "moe_all"])
+def test_single_layer_prompt(ctx, layer, f32):
+    cfg = config([layer], width=32)
+    W = weights(cfg, seed=3)
+    toks = tokens(37, cfg["vocab"], 1)
+    m = build(ctx, cfg, W, f32)
+    got, _ = m.forward_rows(toks, 0, rows=list(range(len(toks))))
+    assert close(got, oracle(cfg, W, toks), f32)
+    m.close()
+
+
+@pytest.mark.parametrize("side", [0, 6])
+def test_side_input_and_depth_average(ctx, side):
+    """three thin layers: a large side embedding (a wrong slice or token shows) and depth weights far from (0, .., 0, 1)"""
+    cfg = config([(gla(heads=1, dim=8, vdim=8), None)] * 3, width=32, side=side)
+    W = weights(cfg, seed=21, side_gain=4.0)
+    for i in range(3):
+        W["l%d.dwa" % i] = bf16_grid(torch.linspace(0.7, -0.4, i + 2))
+    toks = tokens(20, cfg["vocab"], 2)
+    m = build(ctx, cfg, W, True)
+    assert rel(run_cut(m, toks, [9, 2]), oracle(cfg, W, toks)) < TOL[True]
+    m.close()
+
+
+# ------------------------------------------------------------------------------------------------------------ whole stacks
+@pytest.mark.parametrize("f32", [True, False])
+def test_stack_prompt_and_decode(ctx, f32):
+    """a prompt in one step, then token by token: both equal the oracle; the first tokens of a sequence decoded one by one as well"""
+    cfg = config(FULL)
+    W = weights(cfg, seed=5)
+    toks = tokens(90, cfg["vocab"], 2)
+    want = oracle(cfg, W, toks)
+    m = build(ctx, cfg, W, f32)
+    assert close(run_cut(m, toks, [64, 26]), want, f32)          # two panels
+    assert close(run_cut(m, toks, [50]), want, f32)              # 50 at once, 40 decoded (graph replay from the second step on)
+    assert close(run_cut(m, toks[:12], []), want[:12], f32)       # from the very first token one by one
+    m.close()
+
+
+@pytest.mark.parametrize("f32", [True, False])
+def test_wide_panels(ctx, f32):
+    """panels of up to 192 tokens: the matmuls take their tile kernels, the router its many-token dispatch"""
+    cfg = config(FULL)
+    W = weights(cfg, seed=13)
+    toks = tokens(230, cfg["vocab"], 12)
+    m = build(ctx, cfg, W, f32, panel=192)
+    assert close(run_cut(m, toks, [192, 17, 2]), oracle(cfg, W, toks), f32)
+    m.close()
+
+
+@pytest.mark.parametrize("f32", [True, False])
+def test_widths_the_tuned_matmuls_take(ctx, f32):
+    """width 128 and extents that are multiples of 16: in bf16 the dense projections run on the tensor-core kernels of the other models"""
+    cfg = config([(delta(heads=4, kv_heads=2, dim=16, vdim=32, a_rank=16, g_rank=16), dense(256)),
+                  (pair(heads=4, kv_heads=2, dim=32, vdim=32, width=128, blocks=2), moe(experts=4, top=2, ff=128)),
+                  (gla(heads=2, dim=64, vdim=64, a_rank=16), None)], width=128, vocab=160, side=16)
+    W = weights(cfg, seed=14)
+    toks = tokens(100, cfg["vocab"], 15)
+    m = build(ctx, cfg, W, f32, panel=96, logit_rows=96)
+    assert close(run_cut(m, toks, [96, 2]), oracle(cfg, W, toks), f32)
+    m.close()
+
+
+def test_portions_of_many_sizes(ctx):
+    cfg = config(FULL)
+    W = weights(cfg, seed=6)
+    toks = tokens(131, cfg["vocab"], 3)
+    want = oracle(cfg, W, toks)
+    m = build(ctx, cfg, W, True)
+    for cuts in ([2, 2, 3, 2, 64, 2, 31, 2, 17], [1, 2, 1, 63, 64, 1], [7] * 19, [64, 64, 2], [3, 1, 1, 2, 5, 64, 2, 2, 2, 40]):
+        assert rel(run_cut(m, toks, cuts), want) < TOL[True], cuts
+    m.close()
+
+
+def test_slots_reused_and_interleaved(ctx):
+    """two requests advance alternately in two slots; a released slot is taken by a new request and nothing of the old one shows"""
+    cfg = config(FULL)
+    W = weights(cfg, seed=7)
+    a, b, c = tokens(70, cfg["vocab"], 4), tokens(45, cfg["vocab"], 5), tokens(20, cfg["vocab"], 6)
+    wa, wb, wc = oracle(cfg, W, a), oracle(cfg, W, b), oracle(cfg, W, c)
+    m = build(ctx, cfg, W, True, slots=2)
+    sa, sb = m.acquire_slot(), m.acquire_slot()
+    assert {sa, sb} == {0, 1}
+    with pytest.raises(kf.KoifishError):
+        m.acquire_slot()
+    ga, gb, ia, ib = [], [], 0, 0
+    for na, nb in [(30, 2), (1, 20), (2, 1), (37, 22)]:
+        lg, _ = m.forward_rows(a[ia:ia + na], ia, slot=sa, rows=list(range(na)))
+        ga.append(lg), (ia := ia + na)
+        lg, _ = m.forward_rows(b[ib:ib + nb], ib, slot=sb, rows=list(range(nb)))
+        gb.append(lg), (ib := ib + nb)
+    assert rel(np.concatenate(ga), wa) < TOL[True] and rel(np.concatenate(gb), wb) < TOL[True]
+    m.release_slot(sa)
+    with pytest.raises(kf.KoifishError):
+        m.release_slot(sa)
+    sc = m.acquire_slot()
+    assert sc == sa  # the slot that held the 70-token request, state, tails and rows still in place
+    assert rel(run_cut(m, c, [3, 2], slot=sc), wc) < TOL[True]
+    m.close()
+
+
+def test_batched_decode_of_unequal_requests(ctx):
+    """three sequences of different lengths take one token each in one step: every row equals the sequence run alone"""
+    cfg = config(FULL)
+    W = weights(cfg, seed=8)
+    seqs = [tokens(n, cfg["vocab"], 10 + n) for n in (41, 7, 18)]
+    m = build(ctx, cfg, W, True, slots=3)
+    for s, t in enumerate(seqs):
+        m.forward_rows(t[:-4], 0, slot=s)
+    for k in range(4, 0, -1):
+        lg, _ = m.forward_batch([t[len(t) - k] for t in seqs], [len(t) - k for t in seqs])
+        for s, t in enumerate(seqs):
+            assert rel(lg[s], oracle(cfg, W, t)[len(t) - k]) < TOL[True], (s, k)
+    m.close()
+
+
+# ------------------------------------------------------------------------------------------------------------ shaped weights
+@pytest.mark.parametrize("f32", [True, False])
+def test_far_keys_and_the_temperature_steps(ctx, f32):
+    """peaked softmax over 600 positions (queries x 8, a light distance penalty): the key that wins is anywhere, often far back; a mask one
+    position off, a lost first token, a temperature that steps at the wrong position or a penalty left out moves the logits far beyond
+    the gate.  Prompt panels and decoded tokens; the temperature steps every 64 positions, also inside the decoded part."""
+    cfg = config([(pair(heads=4, kv_heads=2, dim=16, vdim=12, coef=0.8, every=64), None), (pair(every=7), moe())])
+    W = weights(cfg, seed=9, q_gain=8.0, r1=0.3)
+    toks = tokens(600, cfg["vocab"], 7)
+    want = oracle(cfg, W, toks)
+    W2 = {k: (v * 0.0 if k.endswith("left.r1") else v) for k, v in W.items()}
+    assert rel(oracle(cfg, W2, toks), want) > 5 * TOL[f32]  # the shaping works: the penalty matters
+    cfg3 = json.loads(json.dumps(cfg))
+    cfg3["layers"][0]["mixer"]["left"]["q_temp"]["every"] = 65
+    assert rel(oracle(cfg3, W, toks), want) > 5 * TOL[f32]  # ... and so does the place of the temperature's steps
+    m = build(ctx, cfg, W, f32, max_seq=640)
+    got = run_cut(m, toks, [64] * 8 + [2, 2, 3, 29])  # 512 in panels, small portions up to 548, then 52 decoded (a step at 575 / 576)
+    assert close(got, want, f32)
+    m.close()
+
+
+def test_slow_decay_keeps_the_first_tokens(ctx):
+    """decays close to 1 in all three recurrences: the state after 300 tokens still holds the first ones; cutting the sequence anywhere,
+    also inside the convolutions' reach of a cut, leaves the logits alone"""
+    cfg = config([(delta(conv=4), None), (gla(tau=64.0), None), (pair(conv=4), moe(experts=4, top=2, ff=8))])
+    W = weights(cfg, seed=10, a_log=-7.0, lam=-9.0, gla_bias=5.0)
+    toks = tokens(300, cfg["vocab"], 8)
+    want = oracle(cfg, W, toks)
+    other = list(toks)
+    other[0] = (toks[0] + 1) % cfg["vocab"]
+    assert rel(oracle(cfg, W, other)[-1], want[-1]) > 10 * TOL[True]  # the last logits do depend on the first token
+    m = build(ctx, cfg, W, True, max_seq=320)
+    assert rel(run_cut(m, toks, [64, 64, 1, 2, 1, 1, 3, 64, 2]), want) < TOL[True]  # ... then 98 decoded one by one
+    m.close()
+
+
+# ------------------------------------------------------------------------------------------------------------ entry points
+def test_greedy_generation(ctx):
+    cfg = config(FULL)
+    W = weights(cfg, seed=11)
+    prompt = tokens(70, cfg["vocab"], 9)  # longer than a panel
+    seq = list(prompt)
+    for _ in range(12):
+        seq.append(int(np.argmax(oracle(cfg, W, seq)[-1])))
+    m = build(ctx, cfg, W, True)
+    out, why = m.generate(prompt, 12)
+    assert out == seq[len(prompt):] and why == 2
+    m.close()
+
+
+def test_command_line_on_a_checkpoint_folder(ctx, tmp_path):
+    """config.json + model.safetensors on disk (the low ranks come from the tensors' shapes, not from the config) -> `generate` and
+    `trace` of the command line, both number formats"""
+    cfg = config(FULL[:3])
+    W = weights(cfg, seed=12)
+    disk = json.loads(json.dumps(cfg))
+    for ly in disk["layers"]:
+        ly["mixer"].pop("a_rank", None), ly["mixer"].pop("g_rank", None)
+    d = tmp_path / "ckpt"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(disk))
+    write_safetensors(str(d / "model.safetensors"), [(k, "BF16", bits(v).reshape(v.shape)) for k, v in W.items()])
+    a, b = tokens(75, cfg["vocab"], 13), tokens(9, cfg["vocab"], 14)
+    wa, wb = oracle(cfg, W, a), oracle(cfg, W, b)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": a[:70], "want": [0, 5, 69]}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": a[70:72], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "x", "tokens": a[72:], "want": [2, 1]}], "end": ["x"]},
+             {"step": 3, "entries": [{"id": "y", "tokens": b, "want": [8]}], "end": ["y"]}]
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    for dtype in ("float32", "bfloat16"):
+        out = tmp_path / ("out_" + dtype)
+        r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", str(d), "--dtype", dtype, "--out", str(out), "--max-tokens", "128"],
+                           input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, env=env, timeout=900)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+        assert not (out / "1.f32").exists()
+        f = lambda n: np.fromfile(str(out / ("%d.f32" % n)), dtype="<f4").reshape(-1, cfg["vocab"])
+        assert close(np.concatenate([f(0), f(2), f(3)]), np.concatenate([wa[[0, 5, 69]], wa[[74, 73]], wb[[8]]]), dtype == "float32")
+    r = subprocess.run([sys.executable, "-m", "koifish_b200.cli", "generate", "--model", str(d), "--ids", ",".join(map(str, b)), "--max-new-tokens", "5"],
+                       capture_output=True, text=True, env=env, cwd=ROOT, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    seq = list(b)
+    for _ in range(5):
+        seq.append(int(np.argmax(oracle(cfg, W, seq)[-1])))
+    got = json.loads(r.stdout.strip().splitlines()[-1])["tokens"]
+    assert len(got) == 5 and got[0] == seq[len(b)]  # bf16 serving: the first token is far from a tie; later ones may legitimately differ
