@@ -306,6 +306,9 @@ int kf_group_rmsnorm_ex(kf_ctx* ctx, void* out_dev, int out_kind, int ldo, float
 int kf_moe_route_ex(kf_ctx* ctx, int32_t* idx_dev, float* wgt_dev, int32_t* offsets_dev, int32_t* entry_slot_dev, int32_t* slot_row_dev,
                     int32_t* slot_group_dev, int32_t* work_dev, const float* logits_dev, int ldl, const void* bias_bf16_dev, int M, int E, int top,
                     int full_softmax);
+/* kf_moe_combine that may add to out instead of writing it (accumulate 1) */
+int kf_moe_combine_ex(kf_ctx* ctx, float* out_dev, const float* y_slots_dev, const int32_t* entry_slot_dev, const float* wgt_dev, const float* shared_dev,
+                      const float* shared_gate_logit_dev, int ld_gate, int M, int dim, int top, int accumulate);
 /* kf_linear_grouped with an activation on the result written in the activation type: act 2 = relu squared (0: float result, no activation) */
 int kf_linear_grouped_act(kf_ctx* ctx, void* y_dev, int ldy, const void* const* w_table_dev, int n_groups, int N, int K, const void* x_dev, int act_f32,
                           int ldx, const int32_t* offsets_dev, const int32_t* slot_group_dev, const int32_t* src_row_dev, int slots, int act);
@@ -328,6 +331,13 @@ int kf_kv_append(kf_ctx* ctx, void* cache_dev, int cache_f32, size_t slot_stride
 int kf_attn_bias(kf_ctx* ctx, void* out_dev, int out_f32, int ldo, const float* q_dev, int ldq, const float* gate_logit_dev, int ldg, const void* cache_dev,
                  int cache_f32, size_t slot_stride, const void* r1_bf16_dev, const void* r2_bf16_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M,
                  int H, int G, int dk, int dv, float scale, float t_coef, int t_every);
+/* the same attention for a panel of M consecutive tokens of one slot on the tensor cores (bf16 cache, dk == dv in {64, 128}) */
+int kf_attn_bias_prefill(kf_ctx* ctx, void* out_bf16_dev, const void* q_bf16_dev, const void* cache_dev, size_t slot_stride, const void* r1_bf16_dev,
+                         const void* r2_bf16_dev, const float* gate_logit_dev, int ldg, const int32_t* pos_dev, const int32_t* slot_dev, int M, int n_head,
+                         int n_kv, int hd, int max_seq, float scale);
+int kf_attn_bias_panel(kf_ctx* ctx, void* out_bf16_dev, void* q_work_bf16_dev, const float* q_dev, int ldq, const float* gate_logit_dev, int ldg,
+                       const void* cache_dev, size_t slot_stride, const void* r1_bf16_dev, const void* r2_bf16_dev, const int32_t* pos_dev,
+                       const int32_t* slot_dev, int M, int H, int G, int hd, int max_seq, float scale, float t_coef, int t_every);
 
 #ifdef __cplusplus
 }

@@ -542,11 +542,24 @@ constexpr int kPfQ = 64, kPfKV = 64;
 #define KF_PF_MINB 2
 #endif
 
-template <int HD, int BKV>
+// BIAS = true: the same tile loop for attention whose score is  scale * (q.k) - r1_h * ln(1 + r2_h * (i - j))  (a logarithmic distance
+// penalty per head; q arrives with its position's temperature folded in), over a cache whose rows hold keys and values of one position
+// side by side (kv_stride elements apart) in the slot slot[0]; the softmax weights enter P.V as hi + lo bf16 parts (16 bits kept), and
+// the result is multiplied by sigmoid(gate) before it is stored.
+struct PfBias {
+    const uint16_t *r1, *r2;  // bf16 [n_head]
+    const float* gate;        // float [M][ldg] logits, heads x HD, or NULL
+    int ldg;
+    const int32_t* slot;
+    size_t slot_stride;       // elements per slot
+    int kv_stride;            // elements between consecutive positions
+    float scale;
+};
+template <int HD, int BKV, bool BIAS>
 __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ q,
                                                               const uint16_t* __restrict__ kc, const uint16_t* __restrict__ vc,
                                                               const int32_t* __restrict__ pos_dev, int M, int n_head, int n_kv, int max_seq,
-                                                              float sqrt_hd) {
+                                                              float sqrt_hd, PfBias xb) {
     constexpr int CH = HD / 8;  // 16-byte chunks per row
     extern __shared__ __align__(16) uint8_t pf_smem[];
     const uint32_t sQ = (uint32_t)__cvta_generic_to_shared(pf_smem);
@@ -554,8 +567,10 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
     const uint32_t sV = sK + 2 * BKV * HD * 2;       // two V tiles
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy (late) query tiles first
-    const int h = blockIdx.y, kvh = h / (n_head / n_kv), kv_dim = n_kv * HD, q_dim = n_head * HD;
+    const int h = blockIdx.y, kvh = h / (n_head / n_kv), kv_dim = BIAS ? xb.kv_stride : n_kv * HD, q_dim = n_head * HD;
     const int pos0 = pos_dev[0];
+    if (BIAS) kc += (size_t)xb.slot[0] * xb.slot_stride, vc += (size_t)xb.slot[0] * xb.slot_stride;
+    const float pen1 = BIAS ? bf16_bits_to_f32(xb.r1[h]) : 0.f, pen2 = BIAS ? bf16_bits_to_f32(xb.r2[h]) : 0.f;
     const int q0 = qt * kPfQ;
     const int kv_len = pos0 + min(M, q0 + kPfQ);  // rows visible to the last query row of this tile
     const int ntiles = (kv_len + BKV - 1) / BKV;
@@ -584,7 +599,8 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
     for (int j = 0; j < HD / 8; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
     const int p_lo = pos0 + q0 + warp * 16 + g, p_hi = p_lo + 8;  // positions of this thread's two query rows
-    const float SC = 1.4426950408889634f / sqrt_hd;  // softmax((q.k)/sqrt(hd)) = 2^((q.k - max) * log2(e)/sqrt(hd)) / sum
+    // softmax((q.k)/sqrt(hd)) = 2^((q.k - max) * log2(e)/sqrt(hd)) / sum ; BIAS: the scores are brought to the log2 domain where the penalty joins
+    const float SC = BIAS ? 1.f : 1.4426950408889634f / sqrt_hd, SCB = xb.scale * 1.4426950408889634f;
 
     for (int kt = 0; kt < ntiles; kt++) {
         const int buf = kt & 1;
@@ -619,7 +635,10 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 float v = sc[j][e];  // raw q.k; 1/sqrt(hd) is folded into the exponent below (the max is scale invariant)
-                if (diag) {
+                if (BIAS) {
+                    const int dist = ((e & 2) ? p_hi : p_lo) - (kt * BKV + j * 8 + 2 * t4 + (e & 1));
+                    v = dist < 0 ? -INFINITY : fmaf(v, SCB, -pen1 * __log2f(fmaf(pen2, (float)dist, 1.f)));
+                } else if (diag) {
                     const int tcol = kt * BKV + j * 8 + 2 * t4 + (e & 1);
                     if (tcol > ((e & 2) ? p_hi : p_lo)) v = -INFINITY;
                 }
@@ -635,14 +654,19 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
         const float c_lo = exp2f((m_lo - base_lo) * SC), c_hi = exp2f((m_hi - base_hi) * SC);
         m_lo = mn_lo, m_hi = mn_hi;
         float rs_lo = 0.f, rs_hi = 0.f;
-        uint32_t pa[BKV / 16][4];
+        uint32_t pa[BKV / 16][4], pb[BIAS ? BKV / 16 : 1][4];
 #pragma unroll
         for (int j = 0; j < BKV / 8; j++) {
             const float p0 = exp2f((sc[j][0] - base_lo) * SC), p1 = exp2f((sc[j][1] - base_lo) * SC);
             const float p2 = exp2f((sc[j][2] - base_hi) * SC), p3 = exp2f((sc[j][3] - base_hi) * SC);
             rs_lo += p0 + p1, rs_hi += p2 + p3;
-            pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16x2(p0, p1);  // A fragment of P for the 16 tokens of n-tiles (2i, 2i+1)
-            pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16x2(p2, p3);
+            const uint32_t w01 = pack_bf16x2(p0, p1), w23 = pack_bf16x2(p2, p3);
+            pa[j >> 1][(j & 1) * 2 + 0] = w01;  // A fragment of P for the 16 tokens of n-tiles (2i, 2i+1)
+            pa[j >> 1][(j & 1) * 2 + 1] = w23;
+            if (BIAS) {  // what the rounding dropped, as a second bf16 operand
+                pb[j >> 1][(j & 1) * 2 + 0] = pack_bf16x2(p0 - bf16lo(w01), p1 - bf16hi(w01));
+                pb[j >> 1][(j & 1) * 2 + 1] = pack_bf16x2(p2 - bf16lo(w23), p3 - bf16hi(w23));
+            }
         }
         l_lo = l_lo * c_lo + rs_lo, l_hi = l_hi * c_hi + rs_hi;
 #pragma unroll
@@ -656,6 +680,10 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
                 ldsm_x4_t(b, vb + sw(kc_ * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, jp * 2 + (lane >> 4)));
                 mma_bf16(o[2 * jp], pa[kc_], b[0], b[1]);
                 mma_bf16(o[2 * jp + 1], pa[kc_], b[2], b[3]);
+                if (BIAS) {
+                    mma_bf16(o[2 * jp], pb[kc_], b[0], b[1]);
+                    mma_bf16(o[2 * jp + 1], pb[kc_], b[2], b[3]);
+                }
             }
         }
         __syncthreads();  // the other buffer is refilled at the top of the next iteration
@@ -668,8 +696,19 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
 #pragma unroll
     for (int j = 0; j < HD / 8; j++) {
         const int d = j * 8 + 2 * t4;
-        if (r_lo < M) *reinterpret_cast<uint32_t*>(out + (size_t)r_lo * q_dim + (size_t)h * HD + d) = pack_bf16x2(o[j][0] * i_lo, o[j][1] * i_lo);
-        if (r_hi < M) *reinterpret_cast<uint32_t*>(out + (size_t)r_hi * q_dim + (size_t)h * HD + d) = pack_bf16x2(o[j][2] * i_hi, o[j][3] * i_hi);
+        float g0 = 1.f, g1 = 1.f, g2 = 1.f, g3 = 1.f;
+        if (BIAS && xb.gate) {
+            if (r_lo < M) {
+                const float2 z = *reinterpret_cast<const float2*>(xb.gate + (size_t)r_lo * xb.ldg + h * HD + d);
+                g0 = 1.f / (1.f + expf(-z.x)), g1 = 1.f / (1.f + expf(-z.y));
+            }
+            if (r_hi < M) {
+                const float2 z = *reinterpret_cast<const float2*>(xb.gate + (size_t)r_hi * xb.ldg + h * HD + d);
+                g2 = 1.f / (1.f + expf(-z.x)), g3 = 1.f / (1.f + expf(-z.y));
+            }
+        }
+        if (r_lo < M) *reinterpret_cast<uint32_t*>(out + (size_t)r_lo * q_dim + (size_t)h * HD + d) = pack_bf16x2(o[j][0] * i_lo * g0, o[j][1] * i_lo * g1);
+        if (r_hi < M) *reinterpret_cast<uint32_t*>(out + (size_t)r_hi * q_dim + (size_t)h * HD + d) = pack_bf16x2(o[j][2] * i_hi * g2, o[j][3] * i_hi * g3);
     }
 }
 
@@ -972,19 +1011,53 @@ extern "C" int kf_attn_prefill(kf_ctx* ctx, void* out, const void* q, const void
     if (hd == 128) {
         static bool set[kf_ctx::kMaxDevices] = {};  // function attributes are per device
         if (!set[ctx->device]) {
-            KF_CUDA(ctx, cudaFuncSetAttribute(kf_attn_prefill_kernel<128, KF_PF_BKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            KF_CUDA(ctx, cudaFuncSetAttribute(kf_attn_prefill_kernel<128, KF_PF_BKV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             set[ctx->device] = true;
         }
-        kf_attn_prefill_kernel<128, KF_PF_BKV><<<grid, 128, smem, ctx->stream>>>((uint16_t*)out, (const uint16_t*)q, (const uint16_t*)kc, (const uint16_t*)vc,
-                                                                      pos_dev, M, n_head, n_kv, max_seq, sq);
+        kf_attn_prefill_kernel<128, KF_PF_BKV, false><<<grid, 128, smem, ctx->stream>>>((uint16_t*)out, (const uint16_t*)q, (const uint16_t*)kc, (const uint16_t*)vc,
+                                                                      pos_dev, M, n_head, n_kv, max_seq, sq, PfBias{});
     } else {
         static bool set[kf_ctx::kMaxDevices] = {};  // function attributes are per device
         if (!set[ctx->device]) {
-            KF_CUDA(ctx, cudaFuncSetAttribute(kf_attn_prefill_kernel<64, KF_PF_BKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            KF_CUDA(ctx, cudaFuncSetAttribute(kf_attn_prefill_kernel<64, KF_PF_BKV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             set[ctx->device] = true;
         }
-        kf_attn_prefill_kernel<64, KF_PF_BKV><<<grid, 128, smem, ctx->stream>>>((uint16_t*)out, (const uint16_t*)q, (const uint16_t*)kc, (const uint16_t*)vc,
-                                                                     pos_dev, M, n_head, n_kv, max_seq, sq);
+        kf_attn_prefill_kernel<64, KF_PF_BKV, false><<<grid, 128, smem, ctx->stream>>>((uint16_t*)out, (const uint16_t*)q, (const uint16_t*)kc, (const uint16_t*)vc,
+                                                                     pos_dev, M, n_head, n_kv, max_seq, sq, PfBias{});
+    }
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+
+// The same panel attention with a logarithmic distance penalty, an output gate and a cache of side-by-side key / value rows (see PfBias):
+// q_bf16 [M][n_head * hd] already carries the query temperature; cache rows [slot][pos][n_kv * hd keys | n_kv * hd values] (bf16);
+// out [M][n_head * hd] bf16 = softmax(scale q.k - r1 ln(1 + r2 dist)) V * sigmoid(gate).  The panel's rows must be in the cache.
+extern "C" int kf_attn_bias_prefill(kf_ctx* ctx, void* out, const void* q_bf16, const void* cache, size_t slot_stride, const void* r1_bf16,
+                                    const void* r2_bf16, const float* gate_logit, int ldg, const int32_t* pos_dev, const int32_t* slot_dev, int M,
+                                    int n_head, int n_kv, int hd, int max_seq, float scale) {
+    if (!ctx || !out || !q_bf16 || !cache || !r1_bf16 || !r2_bf16 || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, (hd == 128 || hd == 64) && n_head % n_kv == 0 && M >= 1 && max_seq >= 1 && (!gate_logit || ldg % 2 == 0), "head size 64/128, GQA");
+    const size_t smem = (size_t)(kPfQ + 4 * KF_PF_BKV) * hd * 2;
+    dim3 grid((M + kPfQ - 1) / kPfQ, n_head);
+    PfBias xb = {(const uint16_t*)r1_bf16, (const uint16_t*)r2_bf16, gate_logit, ldg, slot_dev, slot_stride, 2 * n_kv * hd, scale};
+    const uint16_t* kc = (const uint16_t*)cache;
+    const uint16_t* vc = kc + (size_t)n_kv * hd;
+    if (hd == 128) {
+        static bool set[kf_ctx::kMaxDevices] = {};
+        if (!set[ctx->device]) {
+            KF_CUDA(ctx, cudaFuncSetAttribute(kf_attn_prefill_kernel<128, KF_PF_BKV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            set[ctx->device] = true;
+        }
+        kf_attn_prefill_kernel<128, KF_PF_BKV, true><<<grid, 128, smem, ctx->stream>>>((uint16_t*)out, (const uint16_t*)q_bf16, kc, vc, pos_dev, M, n_head, n_kv,
+                                                                                     max_seq, 1.f, xb);
+    } else {
+        static bool set[kf_ctx::kMaxDevices] = {};
+        if (!set[ctx->device]) {
+            KF_CUDA(ctx, cudaFuncSetAttribute(kf_attn_prefill_kernel<64, KF_PF_BKV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            set[ctx->device] = true;
+        }
+        kf_attn_prefill_kernel<64, KF_PF_BKV, true><<<grid, 128, smem, ctx->stream>>>((uint16_t*)out, (const uint16_t*)q_bf16, kc, vc, pos_dev, M, n_head, n_kv,
+                                                                                    max_seq, 1.f, xb);
     }
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;

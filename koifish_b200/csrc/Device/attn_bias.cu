@@ -30,6 +30,14 @@ __global__ void kf_kv_append_kernel(TC* __restrict__ cache, size_t slot_stride, 
     }
 }
 
+// q_out[m][i] = bf16(q[m][i] * t(pos[m])): the query with its position's temperature, as the tensor-core panel kernel takes it
+__global__ void kf_q_temp_kernel(uint16_t* __restrict__ q_out, const float* __restrict__ q, int ldq, const int32_t* __restrict__ pos, int n, float t_coef,
+                                 int t_every) {
+    const int m = blockIdx.x;
+    const float temp = t_every > 0 ? 1.f + t_coef * logf((float)((pos[m] + 1) / t_every) + 1.f) : 1.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) q_out[(size_t)m * n + i] = f32_to_bf16_bits(q[(size_t)m * ldq + i] * temp);
+}
+
 struct AttnArgs {
     void* out;  // [M][ldo] activation type, heads x dv
     int ldo, out_f32;
@@ -168,4 +176,15 @@ extern "C" int kf_attn_bias(kf_ctx* ctx, void* out, int out_f32, int ldo, const 
 #undef KF_AB
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;
+}
+
+// A panel of M consecutive tokens of ONE slot on the tensor cores (kf_attn_bias_prefill of attention.cu): bf16 cache, dk == dv in {64, 128}.
+// q_work: bf16 scratch [M][H * hd].  Same result as kf_attn_bias up to the bf16 rounding of the tempered query.
+extern "C" int kf_attn_bias_panel(kf_ctx* ctx, void* out_bf16, void* q_work_bf16, const float* q, int ldq, const float* gate_logit, int ldg, const void* cache,
+                                  size_t slot_stride, const void* r1_bf16, const void* r2_bf16, const int32_t* pos_dev, const int32_t* slot_dev, int M, int H,
+                                  int G, int hd, int max_seq, float scale, float t_coef, int t_every) {
+    if (!ctx || !out_bf16 || !q_work_bf16 || !q) return KF_ERR_BAD_ARG;
+    kf_q_temp_kernel<<<M, 256, 0, ctx->stream>>>((uint16_t*)q_work_bf16, q, ldq, pos_dev, H * hd, t_coef, t_every);
+    KF_LAUNCH_CHECK(ctx);
+    return kf_attn_bias_prefill(ctx, out_bf16, q_work_bf16, cache, slot_stride, r1_bf16, r2_bf16, gate_logit, ldg, pos_dev, slot_dev, M, H, G, hd, max_seq, scale);
 }

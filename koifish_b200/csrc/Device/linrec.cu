@@ -202,6 +202,7 @@ __global__ void kf_rglru_scan_kernel(TO* __restrict__ out, int ldo, const float*
     float* st = state + (size_t)slot[m0] * state_stride + ch;
     float s = pos[m0] == 0 ? 0.f : *st;
     const float bias = yb ? bf16_bits_to_f32(yb[ch]) : 0.f;
+#pragma unroll 8  // the loads do not depend on the recurrence: eight tokens' worth are in flight at a time
     for (int t = 0; t < T; t++) {
         const size_t m = (size_t)(m0 + t);
         s = fmaf(A[m * width + ch], s, Bv[m * width + ch]);
@@ -230,8 +231,9 @@ extern "C" int kf_gated_scan(kf_ctx* ctx, float* y, int ldy, const float* q, int
     a.unit_qk = unit_qk, a.inv_tau = decay_kind == 0 ? 1.f / tau : 0.f, a.q_scale = q_scale, a.unit_eps = unit_eps;
     int R = 1;
     while (R * NPT < dk) R <<= 1;
-    int PB = std::min(dv, 256 / R);  // at most 256 threads: the per-token chain is latency-bound, more CTAs hide it better than wider ones
-    while (PB > 8 && (long long)H * nseq * ((dv + PB - 1) / PB) < 2 * ctx->sm_count) PB = (PB + 1) / 2;
+    // up to 256 threads per CTA: the per-token chain of a warp is latency-bound and as long whatever the grid, while the staging of a pass (and
+    // the decay's exponentials, formed once per CTA) is shared by the CTA's columns -- so columns are NOT spread over more, thinner CTAs
+    const int PB = std::max(1, std::min(dv, 256 / R));
     const int threads = std::max(32, ((PB * R + 31) / 32) * 32);
     int TB = (int)std::min<size_t>(32, (44 * 1024 / sizeof(float)) / (size_t)(3 * dk + PB + 1));
     TB = std::max(1, std::min(TB, T));

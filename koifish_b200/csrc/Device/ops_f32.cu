@@ -264,14 +264,15 @@ __global__ void kf_moe_slots_kernel(int32_t* __restrict__ entry_slot, int32_t* _
 }
 // out[m] = sum_j wgt[m][j] * y[slot(m, j)]  (+ sigmoid(sg[m]) * shared[m]), choices added in their routing order
 __global__ void kf_moe_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const int32_t* __restrict__ entry_slot,
-                                      const float* __restrict__ wgt, const float* __restrict__ shared, const float* __restrict__ sg, int ldsg, int dim, int top) {
+                                      const float* __restrict__ wgt, const float* __restrict__ shared, const float* __restrict__ sg, int ldsg, int dim, int top,
+                                      int accumulate) {
     const int m = blockIdx.x;
     const float gate = shared ? (sg ? sigmoid_f(sg[(size_t)m * ldsg]) : 1.f) : 0.f;
     for (int d = threadIdx.x; d < dim; d += blockDim.x) {
         float s = 0.f;
         for (int j = 0; j < top; j++) s = fmaf(wgt[(size_t)m * top + j], y[(size_t)entry_slot[(size_t)m * top + j] * dim + d], s);
         if (shared) s = fmaf(gate, shared[(size_t)m * dim + d], s);
-        out[(size_t)m * dim + d] = s;
+        out[(size_t)m * dim + d] = accumulate ? out[(size_t)m * dim + d] + s : s;
     }
 }
 }  // namespace
@@ -402,10 +403,15 @@ extern "C" int kf_moe_route(kf_ctx* ctx, int32_t* idx, float* wgt, int32_t* offs
                             int32_t* work, const float* logits, int ldl, const void* bias_bf16, int M, int E, int top) {
     return kf_moe_route_ex(ctx, idx, wgt, offsets, entry_slot, slot_row, slot_group, work, logits, ldl, bias_bf16, M, E, top, 0);
 }
-extern "C" int kf_moe_combine(kf_ctx* ctx, float* out, const float* y_slots, const int32_t* entry_slot, const float* wgt, const float* shared,
-                              const float* shared_gate_logit, int ld_gate, int M, int dim, int top) {
+// accumulate 1: out += the combination (the residual stream takes the experts' sum directly)
+extern "C" int kf_moe_combine_ex(kf_ctx* ctx, float* out, const float* y_slots, const int32_t* entry_slot, const float* wgt, const float* shared,
+                                 const float* shared_gate_logit, int ld_gate, int M, int dim, int top, int accumulate) {
     if (!ctx || !out || !y_slots || !entry_slot || !wgt) return KF_ERR_BAD_ARG;
-    kf_moe_combine_kernel<<<M, 256, 0, ctx->stream>>>(out, y_slots, entry_slot, wgt, shared, shared_gate_logit, ld_gate, dim, top);
+    kf_moe_combine_kernel<<<M, 256, 0, ctx->stream>>>(out, y_slots, entry_slot, wgt, shared, shared_gate_logit, ld_gate, dim, top, accumulate);
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;
+}
+extern "C" int kf_moe_combine(kf_ctx* ctx, float* out, const float* y_slots, const int32_t* entry_slot, const float* wgt, const float* shared,
+                              const float* shared_gate_logit, int ld_gate, int M, int dim, int top) {
+    return kf_moe_combine_ex(ctx, out, y_slots, entry_slot, wgt, shared, shared_gate_logit, ld_gate, M, dim, top, 0);
 }

@@ -215,9 +215,13 @@ static int BuildKivorax(Fish& f) {
             sl.state_stride = Wd, sl.tail_stride = (size_t)std::max(1, m.lru_conv - 1) * Wd;
             parts = {a->lq, a->lk, a->lv, a->lg, a->ry, a->rx};
             maxV = std::max<size_t>(maxV, Wd), maxA = std::max<size_t>(maxA, std::max(no, Wd)), maxW = std::max<size_t>(maxW, Wd);
+            maxY = std::max<size_t>(maxY, nq);  // the tempered bf16 query of the panel kernel
             blk->pair = std::move(a);
         }
-        if (sl.row_stride) KF_TRY(b.Buf((char**)&sl.rows, (size_t)c.max_batch * sl.row_stride * asz));
+        if (sl.row_stride) {  // zeroed once: the panel kernel may load rows beyond the sequence's end (masked, but they must hold numbers)
+            KF_TRY(b.Buf((char**)&sl.rows, (size_t)c.max_batch * sl.row_stride * asz));
+            KF_TRY(kf_memset(f.ctx, sl.rows, 0, (size_t)c.max_batch * sl.row_stride * asz));
+        }
         if (sl.state_stride) KF_TRY(b.Buf(&sl.state, (size_t)c.max_batch * sl.state_stride * 4));
         if (sl.tail_stride) KF_TRY(b.Buf(&sl.tail, (size_t)c.max_batch * sl.tail_stride * 4));
         f.states.total_bytes += (size_t)c.max_batch * (sl.row_stride * asz + (sl.state_stride + sl.tail_stride) * 4);
@@ -381,8 +385,13 @@ int PairMixer::cuInfer(int M, float* u, int ldu, const int* off) {
     float* x = (float*)f.x;
     // left: this step's keys and values join the slot's rows, then attention over the rows 0 .. pos, gated, projected, normed into x
     KF_TRY(kf_kv_append(f.ctx, sl.rows, ak, sl.row_stride, u + off[1], ldu, nk, u + off[2], ldu, nv, f.d_pos, f.d_slot, M));
-    KF_TRY(kf_attn_bias(f.ctx, s.act, ak, no, u + off[0], ldu, u + off[3], ldu, sl.rows, ak, sl.row_stride, r1->data, r2->data, f.d_pos, f.d_slot, M, m.heads,
-                        m.kv_heads, m.dim, m.vdim, m.scale, m.qt_coef, m.qt_every));
+    // panels of one sequence with head sizes the tensor-core kernel takes go there; everything else (decode, odd sizes, 32-bit) to the general kernel
+    if (!ak && f.panel_consecutive && f.seq_mode == 0 && M >= 16 && m.dim == m.vdim && (m.dim == 64 || m.dim == 128) && ldu % 2 == 0 && off[3] % 2 == 0)
+        KF_TRY(kf_attn_bias_panel(f.ctx, s.act, s.y, u + off[0], ldu, u + off[3], ldu, sl.rows, sl.row_stride, r1->data, r2->data, f.d_pos, f.d_slot, M, m.heads,
+                                  m.kv_heads, m.dim, c.max_seq_len, m.scale, m.qt_coef, m.qt_every));
+    else
+        KF_TRY(kf_attn_bias(f.ctx, s.act, ak, no, u + off[0], ldu, u + off[3], ldu, sl.rows, ak, sl.row_stride, r1->data, r2->data, f.d_pos, f.d_slot, M, m.heads,
+                            m.kv_heads, m.dim, m.vdim, m.scale, m.qt_coef, m.qt_every));
     KF_TRY(Lin(f, s.sub, E, lo, s.act, no, M));
     KF_TRY(kf_group_rmsnorm(f.ctx, nullptr, 2, E, x, 0.5f, s.sub, E, nullptr, 0, nullptr, 0, lout->data, nullptr, M, E, 1, c.norm_rms_eps));
     // right: the convolved branch (its bias joins before the convolution, so the stored tail holds biased inputs), gates, recurrence
@@ -410,8 +419,8 @@ int KvxFF::cuInfer(int M, const float* u, int ldu, int off) {
     const void* const* tb = (const void* const*)tables;
     KF_TRY(kf_linear_grouped_act(f.ctx, s.h1, card.ff, tb, X, card.ff, E, s.hact, ak, E, s.offsets, s.slot_group, s.slot_row, M * top, 2));
     KF_TRY(kf_linear_grouped(f.ctx, s.yslots, E, tb + X, nullptr, X, E, card.ff, s.h1, ak, card.ff, s.offsets, s.slot_group, nullptr, M * top));
-    KF_TRY(kf_moe_combine(f.ctx, s.sub, s.yslots, s.entry_slot, s.wgt, nullptr, nullptr, 0, M, E, top));
-    return AddTo(f, s.sub, nullptr, M);
+    KF_TRY(kf_moe_combine_ex(f.ctx, (float*)f.x, s.yslots, s.entry_slot, s.wgt, nullptr, nullptr, 0, M, E, top, 1));  // straight into the residual
+    return KF_OK;
 }
 
 int KvxBlock::cuInfer(int M) {
@@ -441,12 +450,13 @@ int KvxBlock::cuInfer(int M) {
     if (ff) KF_TRY(ff->cuInfer(M, s.u, cat.rows, off[nmix]));
     if (c.side_dim > 0) {  // per-layer token input: gelu(gate x) * (this layer's slice of the token's side embedding) -> proj -> RMS norm -> x
         const int sd = c.side_dim;
-        const void* xin = x;
-        if (!ak) {
+        if (ak || M <= 16) {  // few tokens: the matmul reads the fp32 residual as it is (one launch less, no rounded copy)
+            kf_tensor_desc dg = side_gate->Desc();
+            KF_TRY(kf_linear_g(f.ctx, s.v, sd, &dg, x, 1, E, M));
+        } else {  // panels: a bf16 copy feeds the tensor-core tiles
             KF_TRY(kf_bias_act(f.ctx, s.hact, 0, E, x, E, nullptr, 0, nullptr, 0, M, E));
-            xin = s.hact;
+            KF_TRY(Lin(f, s.v, sd, side_gate, s.hact, E, M));
         }
-        KF_TRY(Lin(f, s.v, sd, side_gate, xin, E, M));
         KF_TRY(kf_token_gate(f.ctx, s.mid, ak, sd, s.v, sd, f.tensors["side.embed"]->data, L * sd, layer * sd, f.d_tokens, M, sd));
         KF_TRY(Lin(f, s.sub, E, side_proj, s.mid, sd, M));
         KF_TRY(kf_group_rmsnorm(f.ctx, nullptr, 2, E, x, 1.f, s.sub, E, nullptr, 0, nullptr, 0, side_norm->data, nullptr, M, E, 1, c.norm_rms_eps));

@@ -159,6 +159,19 @@ def test_widths_the_tuned_matmuls_take(ctx, f32):
     m.close()
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+def test_panel_attention_on_tensor_cores(ctx, hd):
+    """bf16, key size = value size = 64 / 128: panels of 16 tokens and more run the tile kernel (peaked softmax, temperature stepping every
+    32 positions, panels that start inside a 64-row tile); smaller portions and decoded tokens the general kernel, on the same cache rows"""
+    cfg = config([(pair(heads=4, kv_heads=2, dim=hd, vdim=hd, coef=0.7, every=32, width=32, blocks=2), None)], width=64, vocab=80)
+    W = weights(cfg, seed=16, q_gain=5.0, r1=0.4)
+    toks = tokens(260, cfg["vocab"], 17)
+    want = oracle(cfg, W, toks)
+    m = build(ctx, cfg, W, False, max_seq=320)
+    assert close(run_cut(m, toks, [64, 17, 3, 64, 30, 2, 16, 40]), want, False)
+    m.close()
+
+
 def test_portions_of_many_sizes(ctx):
     cfg = config(FULL)
     W = weights(cfg, seed=6)
