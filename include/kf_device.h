@@ -330,7 +330,7 @@ int kf_kv_append(kf_ctx* ctx, void* cache_dev, int cache_f32, size_t slot_stride
                  const int32_t* pos_dev, const int32_t* slot_dev, int M);
 int kf_attn_bias(kf_ctx* ctx, void* out_dev, int out_f32, int ldo, const float* q_dev, int ldq, const float* gate_logit_dev, int ldg, const void* cache_dev,
                  int cache_f32, size_t slot_stride, const void* r1_bf16_dev, const void* r2_bf16_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M,
-                 int H, int G, int dk, int dv, float scale, float t_coef, int t_every);
+                 int H, int G, int dk, int dv, float scale, float t_coef, int t_every, int max_pos_hint);
 /* the same attention for a panel of M consecutive tokens of one slot on the tensor cores (bf16 cache, dk == dv in {64, 128}) */
 int kf_attn_bias_prefill(kf_ctx* ctx, void* out_bf16_dev, const void* q_bf16_dev, const void* cache_dev, size_t slot_stride, const void* r1_bf16_dev,
                          const void* r2_bf16_dev, const float* gate_logit_dev, int ldg, const int32_t* pos_dev, const int32_t* slot_dev, int M, int n_head,

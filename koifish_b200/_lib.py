@@ -111,6 +111,21 @@ SIGNATURES = {
     "kf_latent_append": (_I, [_P, _P, _I, _SZ, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F]),
     "kf_latent_attention": (_I, [_P, _P, _P, _P, _I, _P, _P, _P, _I, _SZ, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I]),
     "kf_latent_expand": (_I, [_P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I]),
+    "kf_embed_f32_scaled": (_I, [_P, _P, _P, _DESCP, _P, _I, _F]),
+    "kf_bias_act": (_I, [_P, _P, _I, _I, _P, _I, _P, _I, _P, _I, _I, _I]),
+    "kf_token_gate": (_I, [_P, _P, _I, _I, _P, _I, _P, _I, _I, _P, _I, _I]),
+    "kf_depth_mix": (_I, [_P, _P, _P, _SZ, _P, _I, _SZ]),
+    "kf_group_rmsnorm_ex": (_I, [_P, _P, _I, _I, _P, _F, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _F]),
+    "kf_moe_route_ex": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I]),
+    "kf_moe_combine_ex": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I]),
+    "kf_linear_grouped_act": (_I, [_P, _P, _I, _P, _I, _I, _I, _P, _I, _I, _P, _P, _P, _I, _I]),
+    "kf_conv1d": (_I, [_P, _P, _P, _I, _I, _P, _P, _P, _SZ, _P, _P, _I, _I, _I, _I, _I]),
+    "kf_gated_scan": (_I, [_P, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _P, _SZ, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _F, _F]),
+    "kf_rglru": (_I, [_P, _P, _I, _I, _P, _P, _I, _P, _P, _P, _P, _P, _F, _P, _I, _P, _P, _SZ, _P, _P, _I, _I, _I, _I]),
+    "kf_kv_append": (_I, [_P, _P, _I, _SZ, _P, _I, _I, _P, _I, _I, _P, _P, _I]),
+    "kf_attn_bias": (_I, [_P, _P, _I, _I, _P, _I, _P, _I, _P, _I, _SZ, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I]),
+    "kf_attn_bias_prefill": (_I, [_P, _P, _P, _P, _SZ, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F]),
+    "kf_attn_bias_panel": (_I, [_P, _P, _P, _P, _I, _P, _I, _P, _SZ, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I]),
     "kf_nccl_unique_id": (_I, [_P]),
     "kf_ctx_init_nccl": (_I, [_P, _P, _I, _I]),
     "kf_allreduce_bf16": (_I, [_P, _P, _SZ]),

@@ -8,6 +8,8 @@
 // is written in the activation type.  Beside kf_attn_* of attention.cu (rotated, head size 64 / 128, bf16 only, Qwen3's path).
 #include <math.h>
 
+#include <algorithm>
+
 #include "kf_common.cuh"
 
 namespace {
@@ -52,6 +54,8 @@ struct AttnArgs {
     int H, G, dk, dv;
     float scale, t_coef;
     int t_every;
+    int nsplit;   // the keys of a token are dealt to nsplit CTAs (blockIdx.z); > 1: partial (max, sum, weighted values) go to ws
+    float* ws;    // [M][H][nsplit][dv + 2]
 };
 
 constexpr int AW = 4;  // warps per CTA
@@ -74,10 +78,13 @@ __global__ void __launch_bounds__(AW * 32) kf_attn_bias_kernel(AttnArgs a) {
 #pragma unroll
     for (int i = 0; i < VPL; i++) acc[i] = 0.f;
     const bool vec = sizeof(TC) == 2 && a.dk % 8 == 0 && W % 8 == 0 && (a.slot_stride % 8) == 0 && (((uintptr_t)a.cache & 15) == 0);
-    for (int j0 = warp * 32; j0 <= p; j0 += AW * 32) {
+    // this CTA's keys: [j_lo, j_hi), whole 32-key steps per split
+    const int chunk = a.nsplit > 1 ? (((p + a.nsplit) / a.nsplit + 31) & ~31) : p + 1;
+    const int j_lo = blockIdx.z * chunk, j_hi = min(p + 1, j_lo + chunk);
+    for (int j0 = j_lo + warp * 32; j0 < j_hi; j0 += AW * 32) {
         const int j = j0 + lane;
         float s = -INFINITY;
-        if (j <= p) {
+        if (j < j_hi) {
             const TC* kr = base + (size_t)j * W + kh * a.dk;
             float d0 = 0.f, d1 = 0.f;
             if (vec) {
@@ -95,12 +102,12 @@ __global__ void __launch_bounds__(AW * 32) kf_attn_bias_kernel(AttnArgs a) {
             if (a.r1) s -= r1 * log1pf(r2 * (float)(p - j));
         }
         const float bm = warp_max(s), nm = fmaxf(mx, bm);
-        const float corr = expf(mx - nm), pj = j <= p ? expf(s - nm) : 0.f;  // mx = -inf on the first pass: corr = 0
+        const float corr = expf(mx - nm), pj = j < j_hi ? expf(s - nm) : 0.f;  // mx = -inf on the first pass: corr = 0
         l = l * corr + warp_sum(pj);
 #pragma unroll
         for (int i = 0; i < VPL; i++) acc[i] *= corr;
         mx = nm;
-        const int nk = min(32, p - j0 + 1);
+        const int nk = min(32, j_hi - j0);
         for (int t = 0; t < nk; t++) {
             const float pt = __shfl_sync(0xffffffffu, pj, t);
             const TC* vr = base + (size_t)(j0 + t) * W + a.G * a.dk + kh * a.dv;
@@ -122,9 +129,45 @@ __global__ void __launch_bounds__(AW * 32) kf_attn_bias_kernel(AttnArgs a) {
     for (int w = 0; w < AW; w++) M = fmaxf(M, sml[w * 2]);
     float L = 0.f, f[AW];
     for (int w = 0; w < AW; w++) f[w] = sml[w * 2] == -INFINITY ? 0.f : expf(sml[w * 2] - M), L += f[w] * sml[w * 2 + 1];
+    if (a.nsplit > 1) {  // partial result of this split; kf_attn_bias_merge_kernel finishes
+        float* part = a.ws + (((size_t)m * a.H + h) * a.nsplit + blockIdx.z) * (a.dv + 2);
+        if (threadIdx.x == 0) part[0] = M, part[1] = L;
+        for (int d = threadIdx.x; d < a.dv; d += blockDim.x) {
+            float o = 0.f;
+            for (int w = 0; w < AW; w++) o = fmaf(f[w], sacc[w * a.dv + d], o);
+            part[2 + d] = o;
+        }
+        return;
+    }
     for (int d = threadIdx.x; d < a.dv; d += blockDim.x) {
         float o = 0.f;
         for (int w = 0; w < AW; w++) o = fmaf(f[w], sacc[w * a.dv + d], o);
+        o /= L;
+        if (a.gate) {
+            const float z = a.gate[(size_t)m * a.ldg + h * a.dv + d];
+            o *= 1.f / (1.f + expf(-z));
+        }
+        if (a.out_f32) ((float*)a.out)[(size_t)m * a.ldo + h * a.dv + d] = o;
+        else ((uint16_t*)a.out)[(size_t)m * a.ldo + h * a.dv + d] = f32_to_bf16_bits(o);
+    }
+}
+// the splits of one (token, head) merged in split order, gated, written in the activation type
+__global__ void kf_attn_bias_merge_kernel(AttnArgs a) {
+    const int m = blockIdx.x, h = blockIdx.y;
+    const float* part = a.ws + ((size_t)m * a.H + h) * a.nsplit * (a.dv + 2);
+    float M = -INFINITY;
+    for (int z = 0; z < a.nsplit; z++) M = fmaxf(M, part[(size_t)z * (a.dv + 2)]);
+    float L = 0.f;
+    for (int z = 0; z < a.nsplit; z++) {
+        const float mz = part[(size_t)z * (a.dv + 2)];
+        if (mz != -INFINITY) L += expf(mz - M) * part[(size_t)z * (a.dv + 2) + 1];
+    }
+    for (int d = threadIdx.x; d < a.dv; d += blockDim.x) {
+        float o = 0.f;
+        for (int z = 0; z < a.nsplit; z++) {
+            const float mz = part[(size_t)z * (a.dv + 2)];
+            if (mz != -INFINITY) o = fmaf(expf(mz - M), part[(size_t)z * (a.dv + 2) + 2 + d], o);
+        }
         o /= L;
         if (a.gate) {
             const float z = a.gate[(size_t)m * a.ldg + h * a.dv + d];
@@ -147,10 +190,11 @@ extern "C" int kf_kv_append(kf_ctx* ctx, void* cache, int cache_f32, size_t slot
     return KF_OK;
 }
 // out [M][ldo] (heads x dv, activation type) = attention of token m over the rows 0 .. pos[m] of its slot (its own row appended before).
-// r1 / r2: bf16 [H] distance-penalty numbers or NULL; t_every <= 0: no query temperature; gate_logit: float [M][ldg] or NULL.
+// r1 / r2: bf16 [H] distance-penalty numbers or NULL; t_every <= 0: no query temperature; gate_logit: float [M][ldg] or NULL;
+// max_pos_hint: an upper bound of pos[] (sizes the split of the keys over CTAs; the result does not depend on it beyond rounding).
 extern "C" int kf_attn_bias(kf_ctx* ctx, void* out, int out_f32, int ldo, const float* q, int ldq, const float* gate_logit, int ldg, const void* cache,
                             int cache_f32, size_t slot_stride, const void* r1_bf16, const void* r2_bf16, const int32_t* pos_dev, const int32_t* slot_dev,
-                            int M, int H, int G, int dk, int dv, float scale, float t_coef, int t_every) {
+                            int M, int H, int G, int dk, int dv, float scale, float t_coef, int t_every, int max_pos_hint) {
     if (!ctx || !out || !q || !cache || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, M >= 1 && H >= 1 && G >= 1 && H % G == 0 && dk >= 1 && dv >= 1 && dv <= 512 && (!r1_bf16) == (!r2_bf16), "value size <= 512, kv heads divide heads");
     AttnArgs a = {};
@@ -159,7 +203,16 @@ extern "C" int kf_attn_bias(kf_ctx* ctx, void* out, int out_f32, int ldo, const 
     a.scale = scale, a.t_coef = t_coef, a.t_every = t_every;
     const size_t smem = (size_t)(dk + AW * dv + AW * 2) * sizeof(float);
     KF_REQUIRE(ctx, smem <= 48 * 1024, "key size");
-    dim3 grid(M, H);
+    // few (token, head) pairs and long contexts (decoding): the keys are dealt to several CTAs so that the SMs are busy
+    int nsplit = 1;
+    if (M * H < 2 * ctx->sm_count && max_pos_hint >= 4 * AW * 32)
+        nsplit = std::max(1, std::min(std::min(64, (2 * ctx->sm_count) / (M * H)), (max_pos_hint + 1) / (2 * AW * 32)));
+    if (nsplit > 1) {
+        KF_REQUIRE(ctx, kf_ensure_attn_ws(ctx, (size_t)M * H * nsplit * (dv + 2) * sizeof(float)) == KF_OK, "attention workspace");
+        a.ws = ctx->attn_ws;
+    }
+    a.nsplit = nsplit;
+    dim3 grid(M, H, nsplit);
     const int vpl = (dv + 31) / 32;
 #define KF_AB(TC, V) kf_attn_bias_kernel<TC, V><<<grid, AW * 32, smem, ctx->stream>>>(a)
     if (cache_f32) {
@@ -175,6 +228,10 @@ extern "C" int kf_attn_bias(kf_ctx* ctx, void* out, int out_f32, int ldo, const 
     }
 #undef KF_AB
     KF_LAUNCH_CHECK(ctx);
+    if (nsplit > 1) {
+        kf_attn_bias_merge_kernel<<<dim3(M, H), 128, 0, ctx->stream>>>(a);
+        KF_LAUNCH_CHECK(ctx);
+    }
     return KF_OK;
 }
 

@@ -39,12 +39,14 @@ struct ScanArgs {
     float inv_tau, q_scale, unit_eps;
 };
 
-// grid (heads, sequences, column chunks).  Thread (pl, r) keeps rows n = i * R + r (i < NPT) of state column p0 + pl in registers; the R
-// lanes of a column are adjacent and reduce with shuffles.  TB tokens are staged in shared memory per pass: k, q (normalised there),
-// the decay (formed there), v, beta.
+// grid (heads, sequences, column chunks).  Thread (pl, r) keeps the NPT consecutive rows n = r * NPT + i of state column p0 + pl in
+// registers; the R lanes of a column are adjacent and reduce with shuffles.  TB tokens are staged in shared memory per pass: k, q
+// (normalised there), the decay (formed there), v, beta.  FULL (dk == R * NPT): a thread's slice of k, q and the decay is four 16-byte
+// shared loads each and nothing is bounds-checked; otherwise rows beyond dk read k = q = 0 and leave their (zero) state alone.
 constexpr int NPT = 16;
-__global__ void __launch_bounds__(1024) kf_gated_scan_kernel(ScanArgs a) {
-    extern __shared__ float sm[];
+template <bool DELTA, bool FULL>
+__global__ void __launch_bounds__(256) kf_gated_scan_kernel(ScanArgs a) {
+    extern __shared__ __align__(16) float sm[];
     const int dk = a.dk, TB = a.TB, PB = a.PB, R = a.R;
     float* sK = sm;                  // [TB][dk]
     float* sQ = sK + TB * dk;        // [TB][dk]
@@ -55,15 +57,12 @@ __global__ void __launch_bounds__(1024) kf_gated_scan_kernel(ScanArgs a) {
     const int kh = h / (a.H / a.G);
     const int tid = threadIdx.x, pl = tid / R, r = tid - pl * R, p = p0 + pl;
     const bool live = pl < PB && p < a.dv;
-    const int m0 = seq * a.T;
+    const int m0 = seq * a.T, n0 = r * NPT;
     float* st = a.state + (size_t)a.slot[m0] * a.state_stride + ((size_t)h * a.dv + (live ? p : 0)) * dk;
     const bool fresh = a.pos[m0] == 0;
     float S[NPT];
 #pragma unroll
-    for (int i = 0; i < NPT; i++) {
-        const int n = i * R + r;
-        S[i] = (live && n < dk && !fresh) ? st[n] : 0.f;
-    }
+    for (int i = 0; i < NPT; i++) S[i] = (live && n0 + i < dk && !fresh) ? st[n0 + i] : 0.f;
     const float Aexp = a.decay_kind == 1 ? expf(bf16_bits_to_f32(a.A_log[h])) : 0.f;
     const int warp = tid >> 5, lane = tid & 31, nwarp = blockDim.x >> 5;
     for (int t0 = 0; t0 < a.T; t0 += TB) {
@@ -81,7 +80,7 @@ __global__ void __launch_bounds__(1024) kf_gated_scan_kernel(ScanArgs a) {
             const int tt = i / PB, c = i - tt * PB;
             sV[i] = (p0 + c < a.dv) ? a.v[(size_t)(m0 + t0 + tt) * a.ldv + h * a.dv + p0 + c] : 0.f;
         }
-        if (a.delta)
+        if (DELTA)
             for (int i = tid; i < nt; i += blockDim.x) sB[i] = sigmoid_f(a.beta[(size_t)(m0 + t0 + i) * a.ldb + h]);
         __syncthreads();
         // unit vectors / query scale: one warp per staged token
@@ -100,43 +99,53 @@ __global__ void __launch_bounds__(1024) kf_gated_scan_kernel(ScanArgs a) {
         }
         __syncthreads();
         for (int tt = 0; tt < nt; tt++) {
-            const float* kk = sK + tt * dk;
-            const float* qq = sQ + tt * dk;
-            const float* gg = sG + tt * dk;
-            const float vv = sV[tt * PB + (pl < PB ? pl : 0)];
-            float w = vv;
-            if (a.delta) {
-                float dot = 0.f;
+            float kk[NPT], qq[NPT], gg[NPT];
+            if (FULL) {
+                const float4* k4 = reinterpret_cast<const float4*>(sK + tt * dk + n0);
+                const float4* q4 = reinterpret_cast<const float4*>(sQ + tt * dk + n0);
+                const float4* g4 = reinterpret_cast<const float4*>(sG + tt * dk + n0);
+#pragma unroll
+                for (int j = 0; j < NPT / 4; j++) {
+                    const float4 kv = k4[j], qv = q4[j], gv = g4[j];
+                    kk[4 * j] = kv.x, kk[4 * j + 1] = kv.y, kk[4 * j + 2] = kv.z, kk[4 * j + 3] = kv.w;
+                    qq[4 * j] = qv.x, qq[4 * j + 1] = qv.y, qq[4 * j + 2] = qv.z, qq[4 * j + 3] = qv.w;
+                    gg[4 * j] = gv.x, gg[4 * j + 1] = gv.y, gg[4 * j + 2] = gv.z, gg[4 * j + 3] = gv.w;
+                }
+            } else {
 #pragma unroll
                 for (int i = 0; i < NPT; i++) {
-                    const int n = i * R + r;
-                    if (n < dk) {
-                        S[i] *= gg[n];
-                        dot = fmaf(S[i], kk[n], dot);
-                    }
+                    const bool in = n0 + i < dk;
+                    kk[i] = in ? sK[tt * dk + n0 + i] : 0.f, qq[i] = in ? sQ[tt * dk + n0 + i] : 0.f, gg[i] = in ? sG[tt * dk + n0 + i] : 1.f;
                 }
+            }
+            const float vv = sV[tt * PB + (pl < PB ? pl : 0)];
+            float w = vv;
+            if (DELTA) {
+                float d[4] = {0.f, 0.f, 0.f, 0.f};  // four partial sums: the dependent chain is 4 deep, not 16
+#pragma unroll
+                for (int i = 0; i < NPT; i++) {
+                    S[i] *= gg[i];
+                    d[i & 3] = fmaf(S[i], kk[i], d[i & 3]);
+                }
+                float dot = (d[0] + d[1]) + (d[2] + d[3]);
                 for (int o = R >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
                 w = sB[tt] * (vv - dot);
             }
-            float acc = 0.f;
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < NPT; i++) {
-                const int n = i * R + r;
-                if (n < dk) {
-                    S[i] = a.delta ? fmaf(kk[n], w, S[i]) : fmaf(gg[n], S[i], kk[n] * w);
-                    acc  = fmaf(S[i], qq[n], acc);
-                }
+                S[i]     = DELTA ? fmaf(kk[i], w, S[i]) : fmaf(gg[i], S[i], kk[i] * w);
+                c[i & 3] = fmaf(S[i], qq[i], c[i & 3]);
             }
+            float acc = (c[0] + c[1]) + (c[2] + c[3]);
             for (int o = R >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             if (live && r == 0) a.y[(size_t)(m0 + t0 + tt) * a.ldy + h * a.dv + p] = acc;
         }
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < NPT; i++) {
-            const int n = i * R + r;
-            if (n < dk) st[n] = S[i];
-        }
+        for (int i = 0; i < NPT; i++)
+            if (n0 + i < dk) st[n0 + i] = S[i];
     }
 }
 
@@ -191,26 +200,46 @@ __global__ void __launch_bounds__(128) kf_rglru_gates_kernel(float* __restrict__
         Bv[m * width + ch] = sqrtf(-expm1f(2.f * la)) * ig * u[m * ldu + ch];
     }
 }
-// one thread per (sequence, channel): s <- A s + Bv along the T tokens; out = s * gelu_tanh(y + yb) in the activation type
+// s <- A s + Bv along the T tokens of a sequence, out = s * gelu_tanh(y + yb) in the activation type.  A CTA owns 32 channels (one per
+// lane) and its W warps each a run of consecutive tokens: a first pass reduces every run to one affine map s -> P s + B, the maps of the
+// earlier runs give a warp its incoming state, a second pass replays the run and writes.  Loads are 128-byte rows across the lanes.
+constexpr int LRU_W = 16;
 template <typename TO>
-__global__ void kf_rglru_scan_kernel(TO* __restrict__ out, int ldo, const float* __restrict__ A, const float* __restrict__ Bv, const float* __restrict__ y,
-                                     int ldy, const uint16_t* __restrict__ yb, float* __restrict__ state, size_t state_stride,
-                                     const int32_t* __restrict__ pos, const int32_t* __restrict__ slot, int T, int width) {
-    const int seq = blockIdx.y, ch = blockIdx.x * blockDim.x + threadIdx.x;
-    if (ch >= width) return;
-    const int m0 = seq * T;
-    float* st = state + (size_t)slot[m0] * state_stride + ch;
-    float s = pos[m0] == 0 ? 0.f : *st;
+__global__ void __launch_bounds__(32 * LRU_W) kf_rglru_scan_kernel(TO* __restrict__ out, int ldo, const float* __restrict__ A, const float* __restrict__ Bv,
+                                                                   const float* __restrict__ y, int ldy, const uint16_t* __restrict__ yb,
+                                                                   float* __restrict__ state, size_t state_stride, const int32_t* __restrict__ pos,
+                                                                   const int32_t* __restrict__ slot, int T, int width) {
+    __shared__ float sP[LRU_W][32], sB[LRU_W][32];
+    const int seq = blockIdx.y, lane = threadIdx.x & 31, w = threadIdx.x >> 5, W = blockDim.x >> 5;
+    const int ch = blockIdx.x * 32 + lane, m0 = seq * T;
+    const bool live = ch < width;
+    const int run = (T + W - 1) / W, t_lo = min(T, w * run), t_hi = min(T, t_lo + run);
+    float* st = state + (size_t)slot[m0] * state_stride + (live ? ch : 0);
+    float s = (pos[m0] == 0 || !live) ? 0.f : *st;
+    float P = 1.f, B = 0.f;
+    if (W > 1 && live) {
+#pragma unroll 4
+        for (int t = t_lo; t < t_hi; t++) {
+            const size_t m = (size_t)(m0 + t);
+            const float av = A[m * width + ch];
+            B = fmaf(av, B, Bv[m * width + ch]);
+            P *= av;
+        }
+    }
+    sP[w][lane] = P, sB[w][lane] = B;
+    __syncthreads();
+    for (int q = 0; q < w; q++) s = fmaf(sP[q][lane], s, sB[q][lane]);
+    if (!live) return;
     const float bias = yb ? bf16_bits_to_f32(yb[ch]) : 0.f;
-#pragma unroll 8  // the loads do not depend on the recurrence: eight tokens' worth are in flight at a time
-    for (int t = 0; t < T; t++) {
+#pragma unroll 4
+    for (int t = t_lo; t < t_hi; t++) {
         const size_t m = (size_t)(m0 + t);
         s = fmaf(A[m * width + ch], s, Bv[m * width + ch]);
         const float o = s * gelu_tanh_f(y[m * ldy + ch] + bias);
         if (sizeof(TO) == 2) ((uint16_t*)out)[m * ldo + ch] = f32_to_bf16_bits(o);
         else ((float*)out)[m * ldo + ch] = o;
     }
-    *st = s;
+    if (w == W - 1) *st = s;  // the last run ends at token T - 1 (runs may be empty only at the end when T < W, which the launch rules out)
 }
 }  // namespace
 
@@ -240,7 +269,15 @@ extern "C" int kf_gated_scan(kf_ctx* ctx, float* y, int ldy, const float* q, int
     const size_t smem = (size_t)(3 * TB * dk + TB * PB + TB) * sizeof(float);
     KF_REQUIRE(ctx, smem <= 48 * 1024, "staging area");
     a.R = R, a.PB = PB, a.TB = TB;
-    kf_gated_scan_kernel<<<dim3(H, nseq, (dv + PB - 1) / PB), threads, smem, ctx->stream>>>(a);
+    const dim3 grid(H, nseq, (dv + PB - 1) / PB);
+    const bool full = dk == R * NPT;
+    if (delta) {
+        if (full) kf_gated_scan_kernel<true, true><<<grid, threads, smem, ctx->stream>>>(a);
+        else kf_gated_scan_kernel<true, false><<<grid, threads, smem, ctx->stream>>>(a);
+    } else {
+        if (full) kf_gated_scan_kernel<false, true><<<grid, threads, smem, ctx->stream>>>(a);
+        else kf_gated_scan_kernel<false, false><<<grid, threads, smem, ctx->stream>>>(a);
+    }
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;
 }
@@ -261,12 +298,13 @@ extern "C" int kf_rglru(kf_ctx* ctx, void* out, int out_f32, int ldo, float* wor
         A, Bv, u, ldu, (const uint16_t*)w_r_bf16, (const uint16_t*)b_r_bf16, (const uint16_t*)w_i_bf16, (const uint16_t*)b_i_bf16, (const uint16_t*)lam_bf16, M,
         width, bs, decay_c);
     KF_LAUNCH_CHECK(ctx);
-    dim3 grid((width + 127) / 128, nseq);
+    dim3 grid((width + 31) / 32, nseq);
+    const int warps = std::max(1, std::min(LRU_W, T / 8)), threads = 32 * warps;  // runs of at least 8 tokens; one warp when decoding
     if (out_f32)
-        kf_rglru_scan_kernel<float><<<grid, 128, 0, ctx->stream>>>((float*)out, ldo, A, Bv, y_logit, ldy, (const uint16_t*)y_bias_bf16, state, state_stride, pos_dev,
+        kf_rglru_scan_kernel<float><<<grid, threads, 0, ctx->stream>>>((float*)out, ldo, A, Bv, y_logit, ldy, (const uint16_t*)y_bias_bf16, state, state_stride, pos_dev,
                                                                  slot_dev, T, width);
     else
-        kf_rglru_scan_kernel<uint16_t><<<grid, 128, 0, ctx->stream>>>((uint16_t*)out, ldo, A, Bv, y_logit, ldy, (const uint16_t*)y_bias_bf16, state, state_stride,
+        kf_rglru_scan_kernel<uint16_t><<<grid, threads, 0, ctx->stream>>>((uint16_t*)out, ldo, A, Bv, y_logit, ldy, (const uint16_t*)y_bias_bf16, state, state_stride,
                                                                     pos_dev, slot_dev, T, width);
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;

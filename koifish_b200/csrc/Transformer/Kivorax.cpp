@@ -391,7 +391,7 @@ int PairMixer::cuInfer(int M, float* u, int ldu, const int* off) {
                                   m.kv_heads, m.dim, c.max_seq_len, m.scale, m.qt_coef, m.qt_every));
     else
         KF_TRY(kf_attn_bias(f.ctx, s.act, ak, no, u + off[0], ldu, u + off[3], ldu, sl.rows, ak, sl.row_stride, r1->data, r2->data, f.d_pos, f.d_slot, M, m.heads,
-                            m.kv_heads, m.dim, m.vdim, m.scale, m.qt_coef, m.qt_every));
+                            m.kv_heads, m.dim, m.vdim, m.scale, m.qt_coef, m.qt_every, f.attn_hint));
     KF_TRY(Lin(f, s.sub, E, lo, s.act, no, M));
     KF_TRY(kf_group_rmsnorm(f.ctx, nullptr, 2, E, x, 0.5f, s.sub, E, nullptr, 0, nullptr, 0, lout->data, nullptr, M, E, 1, c.norm_rms_eps));
     // right: the convolved branch (its bias joins before the convolution, so the stored tail holds biased inputs), gates, recurrence
