@@ -108,14 +108,24 @@ __global__ void __launch_bounds__(AW * 32) kf_attn_bias_kernel(AttnArgs a) {
         for (int i = 0; i < VPL; i++) acc[i] *= corr;
         mx = nm;
         const int nk = min(32, j_hi - j0);
-        for (int t = 0; t < nk; t++) {
-            const float pt = __shfl_sync(0xffffffffu, pj, t);
-            const TC* vr = base + (size_t)(j0 + t) * W + a.G * a.dk + kh * a.dv;
+        // U keys per round: their value loads are issued together (a key past the range repeats the last row with weight 0)
+        constexpr int U = VPL <= 4 ? 4 : (VPL <= 8 ? 2 : 1);
+        for (int t = 0; t < nk; t += U) {
+            float pt[U], x[U][VPL];
 #pragma unroll
-            for (int i = 0; i < VPL; i++) {
-                const int d = i * 32 + lane;
-                if (d < a.dv) acc[i] = fmaf(pt, ldc<TC>(vr + d), acc[i]);
+            for (int e = 0; e < U; e++) {
+                pt[e] = __shfl_sync(0xffffffffu, pj, (t + e) & 31);
+                const TC* vr = base + (size_t)min(j0 + t + e, j_hi - 1) * W + a.G * a.dk + kh * a.dv;
+#pragma unroll
+                for (int i = 0; i < VPL; i++) {
+                    const int d = i * 32 + lane;
+                    x[e][i] = d < a.dv ? ldc<TC>(vr + d) : 0.f;
+                }
             }
+#pragma unroll
+            for (int e = 0; e < U; e++)
+#pragma unroll
+                for (int i = 0; i < VPL; i++) acc[i] = fmaf(pt[e], x[e][i], acc[i]);
         }
     }
 #pragma unroll

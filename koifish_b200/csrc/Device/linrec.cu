@@ -68,17 +68,38 @@ __global__ void __launch_bounds__(256) kf_gated_scan_kernel(ScanArgs a) {
     for (int t0 = 0; t0 < a.T; t0 += TB) {
         const int nt = min(TB, a.T - t0);
         __syncthreads();
-        for (int i = tid; i < nt * dk; i += blockDim.x) {
-            const int tt = i / dk, n = i - tt * dk;
-            const size_t m = (size_t)(m0 + t0 + tt);
-            sK[i] = a.k[m * a.ldk + kh * dk + n];
-            sQ[i] = a.q[m * a.ldq + kh * dk + n];
-            const float zz = a.z[m * a.ldz + h * dk + n] + (a.zbias ? bf16_bits_to_f32(a.zbias[h * dk + n]) : 0.f);
-            sG[i] = a.decay_kind == 1 ? expf(-Aexp * softplus_f(zz)) : expf(log_sigmoid_f(zz) * a.inv_tau);
+        // four elements per thread and round: their global loads are issued together, then the decays are formed
+        for (int i0 = tid; i0 < nt * dk; i0 += 4 * blockDim.x) {
+            float kv[4], qv[4], zv[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int i = i0 + e * blockDim.x;
+                if (i < nt * dk) {
+                    const int tt = i / dk, n = i - tt * dk;
+                    const size_t m = (size_t)(m0 + t0 + tt);
+                    kv[e] = a.k[m * a.ldk + kh * dk + n], qv[e] = a.q[m * a.ldq + kh * dk + n];
+                    zv[e] = a.z[m * a.ldz + h * dk + n] + (a.zbias ? bf16_bits_to_f32(a.zbias[h * dk + n]) : 0.f);
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int i = i0 + e * blockDim.x;
+                if (i < nt * dk) {
+                    sK[i] = kv[e], sQ[i] = qv[e];
+                    sG[i] = a.decay_kind == 1 ? expf(-Aexp * softplus_f(zv[e])) : expf(log_sigmoid_f(zv[e]) * a.inv_tau);
+                }
+            }
         }
-        for (int i = tid; i < nt * PB; i += blockDim.x) {
-            const int tt = i / PB, c = i - tt * PB;
-            sV[i] = (p0 + c < a.dv) ? a.v[(size_t)(m0 + t0 + tt) * a.ldv + h * a.dv + p0 + c] : 0.f;
+        for (int i0 = tid; i0 < nt * PB; i0 += 4 * blockDim.x) {
+            float vv[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int i = i0 + e * blockDim.x, tt = i / PB, c = i - tt * PB;
+                vv[e] = (i < nt * PB && p0 + c < a.dv) ? a.v[(size_t)(m0 + t0 + tt) * a.ldv + h * a.dv + p0 + c] : 0.f;
+            }
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                if (i0 + e * blockDim.x < nt * PB) sV[i0 + e * blockDim.x] = vv[e];
         }
         if (DELTA)
             for (int i = tid; i < nt; i += blockDim.x) sB[i] = sigmoid_f(a.beta[(size_t)(m0 + t0 + i) * a.ldb + h]);
