@@ -32,7 +32,7 @@ struct ScanArgs {
     size_t state_stride;
     const int32_t *pos, *slot;
     int T, H, G, dk, dv;
-    int R, PB, TB;
+    int R, PB, TB, dkp;      // dkp: padded length of a staged row
     int delta;               // 1: delta-rule write, 0: plain outer-product write
     int decay_kind;          // 0: sigmoid(z + b)^(1/tau) ; 1: exp(-exp(A_h) softplus(z + b))
     int unit_qk;             // q, k divided by sqrt(sum x^2 + unit_eps) per head
@@ -40,18 +40,21 @@ struct ScanArgs {
 };
 
 // grid (heads, sequences, column chunks).  Thread (pl, r) keeps the NPT consecutive rows n = r * NPT + i of state column p0 + pl in
-// registers (NPT = 16 / 32 / 64: up to 64 key channels sit in ONE thread, so that all lanes of a warp read the same k, q and decay
-// entries -- one shared-memory broadcast per 16 bytes -- and nothing is reduced across lanes; larger key sizes use R = 2, 4, 8 adjacent
-// lanes per column and shuffles).  TB tokens are staged in shared memory per pass: k, q (normalised there), the decay (formed there), v,
-// beta.  FULL (dk == R * NPT): 16-byte shared loads and no bounds checks; otherwise rows beyond dk read k = q = 0 and keep a zero state.
-template <bool DELTA, bool FULL, int NPT>
-__global__ void __launch_bounds__(128) kf_gated_scan_kernel(ScanArgs a) {
+// registers; the R lanes of a column are adjacent and reduce with shuffles.  TB tokens are staged in shared memory per pass: k, q
+// (normalised there), the decay (formed there), v, beta.  FULL (dk == R * NPT): a thread's slice of k, q and the decay is four 16-byte
+// shared loads each and nothing is bounds-checked; otherwise rows beyond dk read k = q = 0 and leave their (zero) state alone.
+constexpr int NPT = 16;
+template <bool DELTA, bool FULL>
+__global__ void __launch_bounds__(256) kf_gated_scan_kernel(ScanArgs a) {
     extern __shared__ __align__(16) float sm[];
-    const int dk = a.dk, TB = a.TB, PB = a.PB, R = a.R;
-    float* sK = sm;                  // [TB][dk]
-    float* sQ = sK + TB * dk;        // [TB][dk]
-    float* sG = sQ + TB * dk;        // [TB][dk]
-    float* sV = sG + TB * dk;        // [TB][PB]
+    // staged rows are padded by 4 floats after every 16: the R lanes of a column read slices 20 floats apart, which fall into different
+    // banks (slices exactly 16 apart would collide two by two)
+    const int dk = a.dk, TB = a.TB, PB = a.PB, R = a.R, dkp = a.dkp;
+    auto ix = [](int n) { return n + ((n >> 4) << 2); };
+    float* sK = sm;                  // [TB][dkp]
+    float* sQ = sK + TB * dkp;       // [TB][dkp]
+    float* sG = sQ + TB * dkp;       // [TB][dkp]
+    float* sV = sG + TB * dkp;       // [TB][PB]
     float* sB = sV + TB * PB;        // [TB]
     const int h = blockIdx.x, seq = blockIdx.y, p0 = blockIdx.z * PB;
     const int kh = h / (a.H / a.G);
@@ -85,8 +88,9 @@ __global__ void __launch_bounds__(128) kf_gated_scan_kernel(ScanArgs a) {
             for (int e = 0; e < 4; e++) {
                 const int i = i0 + e * blockDim.x;
                 if (i < nt * dk) {
-                    sK[i] = kv[e], sQ[i] = qv[e];
-                    sG[i] = a.decay_kind == 1 ? expf(-Aexp * softplus_f(zv[e])) : expf(log_sigmoid_f(zv[e]) * a.inv_tau);
+                    const int tt = i / dk, o = tt * dkp + ix(i - tt * dk);
+                    sK[o] = kv[e], sQ[o] = qv[e];
+                    sG[o] = a.decay_kind == 1 ? expf(-Aexp * softplus_f(zv[e])) : expf(log_sigmoid_f(zv[e]) * a.inv_tau);
                 }
             }
         }
@@ -108,60 +112,58 @@ __global__ void __launch_bounds__(128) kf_gated_scan_kernel(ScanArgs a) {
         for (int tt = warp; tt < nt; tt += nwarp) {
             float sq = 0.f, sk = 0.f;
             if (a.unit_qk) {
-                for (int n = lane; n < dk; n += 32) sq = fmaf(sQ[tt * dk + n], sQ[tt * dk + n], sq), sk = fmaf(sK[tt * dk + n], sK[tt * dk + n], sk);
+                for (int n = lane; n < dk; n += 32) sq = fmaf(sQ[tt * dkp + ix(n)], sQ[tt * dkp + ix(n)], sq), sk = fmaf(sK[tt * dkp + ix(n)], sK[tt * dkp + ix(n)], sk);
                 sq = warp_sum(sq), sk = warp_sum(sk);
             }
             const float fq = a.unit_qk ? a.q_scale / sqrtf(sq + a.unit_eps) : a.q_scale;
             const float fk = a.unit_qk ? 1.f / sqrtf(sk + a.unit_eps) : 1.f;
             for (int n = lane; n < dk; n += 32) {
-                sQ[tt * dk + n] *= fq;
-                if (a.unit_qk) sK[tt * dk + n] *= fk;
+                sQ[tt * dkp + ix(n)] *= fq;
+                if (a.unit_qk) sK[tt * dkp + ix(n)] *= fk;
             }
         }
         __syncthreads();
         for (int tt = 0; tt < nt; tt++) {
-            const float* kr = sK + tt * dk + n0;
-            const float* qr = sQ + tt * dk + n0;
-            const float* gr = sG + tt * dk + n0;
-            // four entries of a staged row starting at row n0 + 4 j of this thread's slice
-            auto ld4 = [&](const float* row, int j, float oob) -> float4 {
-                if (FULL) return reinterpret_cast<const float4*>(row)[j];
-                float4 v;
-                v.x = n0 + 4 * j + 0 < dk ? row[4 * j + 0] : oob, v.y = n0 + 4 * j + 1 < dk ? row[4 * j + 1] : oob;
-                v.z = n0 + 4 * j + 2 < dk ? row[4 * j + 2] : oob, v.w = n0 + 4 * j + 3 < dk ? row[4 * j + 3] : oob;
-                return v;
-            };
+            float kk[NPT], qq[NPT], gg[NPT];
+            if (FULL) {
+                const float4* k4 = reinterpret_cast<const float4*>(sK + tt * dkp + ix(n0));
+                const float4* q4 = reinterpret_cast<const float4*>(sQ + tt * dkp + ix(n0));
+                const float4* g4 = reinterpret_cast<const float4*>(sG + tt * dkp + ix(n0));
+#pragma unroll
+                for (int j = 0; j < NPT / 4; j++) {
+                    const float4 kv = k4[j], qv = q4[j], gv = g4[j];
+                    kk[4 * j] = kv.x, kk[4 * j + 1] = kv.y, kk[4 * j + 2] = kv.z, kk[4 * j + 3] = kv.w;
+                    qq[4 * j] = qv.x, qq[4 * j + 1] = qv.y, qq[4 * j + 2] = qv.z, qq[4 * j + 3] = qv.w;
+                    gg[4 * j] = gv.x, gg[4 * j + 1] = gv.y, gg[4 * j + 2] = gv.z, gg[4 * j + 3] = gv.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < NPT; i++) {
+                    const bool in = n0 + i < dk;
+                    const int o = tt * dkp + ix(n0 + i);
+                    kk[i] = in ? sK[o] : 0.f, qq[i] = in ? sQ[o] : 0.f, gg[i] = in ? sG[o] : 1.f;
+                }
+            }
             const float vv = sV[tt * PB + (pl < PB ? pl : 0)];
             float w = vv;
             if (DELTA) {
-                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;  // four partial sums: short dependent chains
+                float d[4] = {0.f, 0.f, 0.f, 0.f};  // four partial sums: the dependent chain is 4 deep, not 16
 #pragma unroll
-                for (int j = 0; j < NPT / 4; j++) {
-                    const float4 gv = ld4(gr, j, 1.f), kv = ld4(kr, j, 0.f);
-                    S[4 * j + 0] *= gv.x, S[4 * j + 1] *= gv.y, S[4 * j + 2] *= gv.z, S[4 * j + 3] *= gv.w;
-                    d0 = fmaf(S[4 * j + 0], kv.x, d0), d1 = fmaf(S[4 * j + 1], kv.y, d1);
-                    d2 = fmaf(S[4 * j + 2], kv.z, d2), d3 = fmaf(S[4 * j + 3], kv.w, d3);
+                for (int i = 0; i < NPT; i++) {
+                    S[i] *= gg[i];
+                    d[i & 3] = fmaf(S[i], kk[i], d[i & 3]);
                 }
-                float dot = (d0 + d1) + (d2 + d3);
+                float dot = (d[0] + d[1]) + (d[2] + d[3]);
                 for (int o = R >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
                 w = sB[tt] * (vv - dot);
             }
-            float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int j = 0; j < NPT / 4; j++) {
-                const float4 kv = ld4(kr, j, 0.f), qv = ld4(qr, j, 0.f);
-                if (DELTA) {
-                    S[4 * j + 0] = fmaf(kv.x, w, S[4 * j + 0]), S[4 * j + 1] = fmaf(kv.y, w, S[4 * j + 1]);
-                    S[4 * j + 2] = fmaf(kv.z, w, S[4 * j + 2]), S[4 * j + 3] = fmaf(kv.w, w, S[4 * j + 3]);
-                } else {
-                    const float4 gv = ld4(gr, j, 1.f);
-                    S[4 * j + 0] = fmaf(gv.x, S[4 * j + 0], kv.x * w), S[4 * j + 1] = fmaf(gv.y, S[4 * j + 1], kv.y * w);
-                    S[4 * j + 2] = fmaf(gv.z, S[4 * j + 2], kv.z * w), S[4 * j + 3] = fmaf(gv.w, S[4 * j + 3], kv.w * w);
-                }
-                c0 = fmaf(S[4 * j + 0], qv.x, c0), c1 = fmaf(S[4 * j + 1], qv.y, c1);
-                c2 = fmaf(S[4 * j + 2], qv.z, c2), c3 = fmaf(S[4 * j + 3], qv.w, c3);
+            for (int i = 0; i < NPT; i++) {
+                S[i]     = DELTA ? fmaf(kk[i], w, S[i]) : fmaf(gg[i], S[i], kk[i] * w);
+                c[i & 3] = fmaf(S[i], qq[i], c[i & 3]);
             }
-            float acc = (c0 + c1) + (c2 + c3);
+            float acc = (c[0] + c[1]) + (c[2] + c[3]);
             for (int o = R >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             if (live && r == 0) a.y[(size_t)(m0 + t0 + tt) * a.ldy + h * a.dv + p] = acc;
         }
@@ -275,39 +277,34 @@ extern "C" int kf_gated_scan(kf_ctx* ctx, float* y, int ldy, const float* q, int
                              const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int H, int G, int dk, int dv, int delta, int decay_kind,
                              float tau, int unit_qk, float unit_eps, float q_scale) {
     if (!ctx || !y || !q || !k || !v || !z || !state || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
-    KF_REQUIRE(ctx, nseq >= 1 && T >= 1 && H >= 1 && G >= 1 && H % G == 0 && dk >= 1 && dv >= 1 && dk <= 512, "key size <= 512, kv heads divide heads");
+    KF_REQUIRE(ctx, nseq >= 1 && T >= 1 && H >= 1 && G >= 1 && H % G == 0 && dk >= 1 && dv >= 1 && dk <= 32 * NPT, "key size <= 512, kv heads divide heads");
     KF_REQUIRE(ctx, (!delta || beta_logit) && (decay_kind == 0 ? tau > 0.f : A_log_bf16 != nullptr) && state_stride >= (size_t)H * dk * dv, "arguments");
     ScanArgs a = {};
     a.y = y, a.ldy = ldy, a.q = q, a.k = k, a.v = v, a.z = z, a.beta = beta_logit, a.ldq = ldq, a.ldk = ldk, a.ldv = ldv, a.ldz = ldz, a.ldb = ldb;
     a.zbias = (const uint16_t*)zbias_bf16, a.A_log = (const uint16_t*)A_log_bf16, a.state = state, a.state_stride = state_stride;
     a.pos = pos_dev, a.slot = slot_dev, a.T = T, a.H = H, a.G = G, a.dk = dk, a.dv = dv, a.delta = delta, a.decay_kind = decay_kind;
     a.unit_qk = unit_qk, a.inv_tau = decay_kind == 0 ? 1.f / tau : 0.f, a.q_scale = q_scale, a.unit_eps = unit_eps;
-    // rows per thread: the whole key size when it is at most 64 (no lanes to reduce over), else 64 rows in each of R = 2, 4, 8 lanes
-    const int NPT = dk <= 16 ? 16 : dk <= 32 ? 32 : 64;
     int R = 1;
     while (R * NPT < dk) R <<= 1;
-    // up to 128 threads per CTA: the per-token chain of a warp is latency-bound and as long whatever the grid, while the staging of a pass
-    // (and the decay's exponentials, formed once per CTA) is shared by the CTA's columns -- so columns are NOT spread over more, thinner CTAs
-    const int PB = std::max(1, std::min(dv, 128 / R));
+    // up to 256 threads per CTA: the per-token chain of a warp is latency-bound and as long whatever the grid, while the staging of a pass (and
+    // the decay's exponentials, formed once per CTA) is shared by the CTA's columns -- so columns are NOT spread over more, thinner CTAs
+    const int PB = std::max(1, std::min(dv, 256 / R));
     const int threads = std::max(32, ((PB * R + 31) / 32) * 32);
-    int TB = (int)std::min<size_t>(32, (44 * 1024 / sizeof(float)) / (size_t)(3 * dk + PB + 1));
+    const int dkp = ((dk + 15) / 16) * 20;
+    int TB = (int)std::min<size_t>(32, (44 * 1024 / sizeof(float)) / (size_t)(3 * dkp + PB + 1));
     TB = std::max(1, std::min(TB, T));
-    const size_t smem = (size_t)(3 * TB * dk + TB * PB + TB) * sizeof(float);
+    const size_t smem = (size_t)(3 * TB * dkp + TB * PB + TB) * sizeof(float);
     KF_REQUIRE(ctx, smem <= 48 * 1024, "staging area");
-    a.R = R, a.PB = PB, a.TB = TB;
+    a.R = R, a.PB = PB, a.TB = TB, a.dkp = dkp;
     const dim3 grid(H, nseq, (dv + PB - 1) / PB);
     const bool full = dk == R * NPT;
-#define KF_GS(D, F, N) kf_gated_scan_kernel<D, F, N><<<grid, threads, smem, ctx->stream>>>(a)
-#define KF_GS_N(D, F) (NPT == 16 ? KF_GS(D, F, 16) : NPT == 32 ? KF_GS(D, F, 32) : KF_GS(D, F, 64))
     if (delta) {
-        if (full) KF_GS_N(true, true);
-        else KF_GS_N(true, false);
+        if (full) kf_gated_scan_kernel<true, true><<<grid, threads, smem, ctx->stream>>>(a);
+        else kf_gated_scan_kernel<true, false><<<grid, threads, smem, ctx->stream>>>(a);
     } else {
-        if (full) KF_GS_N(false, true);
-        else KF_GS_N(false, false);
+        if (full) kf_gated_scan_kernel<false, true><<<grid, threads, smem, ctx->stream>>>(a);
+        else kf_gated_scan_kernel<false, false><<<grid, threads, smem, ctx->stream>>>(a);
     }
-#undef KF_GS_N
-#undef KF_GS
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;
 }
