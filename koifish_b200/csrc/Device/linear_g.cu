@@ -294,13 +294,16 @@ constexpr int kGemvMaxSlots = 16;
 extern "C" int kf_linear_g(kf_ctx* ctx, float* y, int ldy, const kf_tensor_desc* w, const void* x, int act_f32, int ldx, int M) {
     if (!ctx || !y || !w || !x) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, w->type == KF_T_BF16 && M >= 1 && w->rows >= 1 && w->cols >= 1 && ldx >= w->cols && ldy >= w->rows, "bf16 weight, ld >= extent");
+    // few outputs over a long reduction (a gate or a router of a panel): tiles would leave all but a handful of SMs idle, so every
+    // (token, output) pair gets a warp instead; the weight (<= 64 rows) stays in L2
+    const bool skinny = w->rows <= 64 && w->cols >= 512 && M > kGemvMaxSlots;
     // shapes the tuned kernels take go there (tcgen05 / TMEM panels, the HBM-rate GEMV); fp32 result through their fp32 epilogue
-    if (!act_f32 && ldx == w->cols && ldy == w->rows && w->cols % 128 == 0 && w->rows % 16 == 0 && w->rows >= 16 && ctx->tc_min_m != 0 &&
+    if (!skinny && !act_f32 && ldx == w->cols && ldy == w->rows && w->cols % 128 == 0 && w->rows % 16 == 0 && w->rows >= 16 && ctx->tc_min_m != 0 &&
         (((uintptr_t)w->data_dev | (uintptr_t)x | (uintptr_t)y) & 15) == 0)
         return kf_linear(ctx, y, w, x, M, KF_EPI_F32, nullptr);
     LinArgs a = {};
     a.W0 = (const uint16_t*)w->data_dev, a.x = x, a.y = y, a.M = M, a.N = w->rows, a.K = w->cols, a.ldx = ldx, a.ldy = ldy;
-    return dispatch(ctx, a, M, 1, M <= kGemvMaxSlots, false, act_f32);
+    return dispatch(ctx, a, M, 1, M <= kGemvMaxSlots || skinny, false, act_f32);
 }
 // y = silu(Wg x) * (Wu x), written in the activation type (bf16 bits, or float when act_f32)
 extern "C" int kf_linear_g_swiglu(kf_ctx* ctx, void* y, int ldy, const kf_tensor_desc* wg, const kf_tensor_desc* wu, const void* x, int act_f32,

@@ -450,13 +450,8 @@ int KvxBlock::cuInfer(int M) {
     if (ff) KF_TRY(ff->cuInfer(M, s.u, cat.rows, off[nmix]));
     if (c.side_dim > 0) {  // per-layer token input: gelu(gate x) * (this layer's slice of the token's side embedding) -> proj -> RMS norm -> x
         const int sd = c.side_dim;
-        if (ak || M <= 16) {  // few tokens: the matmul reads the fp32 residual as it is (one launch less, no rounded copy)
-            kf_tensor_desc dg = side_gate->Desc();
-            KF_TRY(kf_linear_g(f.ctx, s.v, sd, &dg, x, 1, E, M));
-        } else {  // panels: a bf16 copy feeds the tensor-core tiles
-            KF_TRY(kf_bias_act(f.ctx, s.hact, 0, E, x, E, nullptr, 0, nullptr, 0, M, E));
-            KF_TRY(Lin(f, s.v, sd, side_gate, s.hact, E, M));
-        }
+        kf_tensor_desc dg = side_gate->Desc();
+        KF_TRY(kf_linear_g(f.ctx, s.v, sd, &dg, x, 1, E, M));  // reads the fp32 residual as it is (no rounded copy) in both number formats
         KF_TRY(kf_token_gate(f.ctx, s.mid, ak, sd, s.v, sd, f.tensors["side.embed"]->data, L * sd, layer * sd, f.d_tokens, M, sd));
         KF_TRY(Lin(f, s.sub, E, side_proj, s.mid, sd, M));
         KF_TRY(kf_group_rmsnorm(f.ctx, nullptr, 2, E, x, 1.f, s.sub, E, nullptr, 0, nullptr, 0, side_norm->data, nullptr, M, E, 1, c.norm_rms_eps));

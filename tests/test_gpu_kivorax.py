@@ -120,6 +120,25 @@ def test_side_input_and_depth_average(ctx, side):
     m.close()
 
 
+def test_few_outputs_over_a_long_reduction(ctx):
+    """kf_linear_g with at most 64 outputs, a reduction of 512 and more and a panel of tokens (a gate of the side input at real widths): the
+    warp-per-output form, bf16 and float activations, against float64"""
+    import ctypes as C
+    rs = np.random.RandomState(0)
+    for (M, N, K) in [(40, 24, 640), (100, 64, 512), (17, 1, 1000), (300, 16, 2048)]:
+        w = bf16_grid(torch.from_numpy(rs.randn(N, K).astype(np.float32)))
+        x = bf16_grid(torch.from_numpy(rs.randn(M, K).astype(np.float32)))
+        wd = ctx.array(bits(w))
+        want = (x.double() @ w.double().T).numpy()
+        for act_f32 in (0, 1):
+            xd = ctx.array(x.numpy() if act_f32 else bits(x))
+            y = ctx.empty(M * N * 4)
+            d = kf.TensorDesc(wd.ptr, None, N, K, kf.KF_T_BF16, 128, 0, None, None)
+            ctx.check(ctx.lib.kf_linear_g(ctx.h, y.ptr, N, C.byref(d), xd.ptr, act_f32, K, M), "kf_linear_g")
+            got = y.numpy(np.float32, (M, N))
+            assert np.abs(got - want).max() <= 2e-5 * np.abs(want).max() + 1e-6, (M, N, K, act_f32)
+
+
 # ------------------------------------------------------------------------------------------------------------ whole stacks
 @pytest.mark.parametrize("f32", [True, False])
 def test_stack_prompt_and_decode(ctx, f32):
