@@ -52,9 +52,9 @@ def kivorax_config(p):
         if ch == "d":
             mixer, typ = dict(heads=k["heads"], kv_heads=k["heads"] // 2, dim=k["dim"], vdim=2 * k["dim"], conv=4, a_rank=k["rank"], g_rank=k["rank"]), "channel_delta"
         elif ch == "g":
-            mixer, typ = dict(heads=k["heads"], dim=k["dim"], vdim=2 * k["dim"], tau=16.0, a_rank=k["rank"]), "gla"
+            mixer, typ = dict(heads=k["heads"], dim=k["dim"], vdim=2 * k["dim"], tau=8.0, a_rank=k["rank"]), "gla"
         else:
-            mixer = dict(left=dict(heads=k["heads"], kv_heads=max(1, k["heads"] // 4), dim=128, vdim=128, scale=128 ** -0.5, q_temp=dict(coef=0.5, every=256)),
+            mixer = dict(left=dict(heads=k["heads"], kv_heads=max(1, k["heads"] // 4), dim=128, vdim=128, scale=128 ** -0.5, q_temp=dict(coef=0.4, every=512)),
                          right=dict(width=w, blocks=k["heads"], conv=4))
             typ = "parallel"
         mlp = {"kind": "dense", "ff": m["top"] * m["ff"]} if i == 0 else {"kind": "moe", "router": {"experts": m["experts"], "top": m["top"]}, "expert": {"ff": m["ff"]}}

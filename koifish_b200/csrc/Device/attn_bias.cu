@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(AW * 32) kf_attn_bias_kernel(AttnArgs a) {
         for (int i = 0; i < VPL; i++) acc[i] *= corr;
         mx = nm;
         const int nk = min(32, j_hi - j0);
-        // U keys per round: their value loads are issued together (a key past the range repeats the last row with weight 0)
+        // U keys per step: their value loads are issued together (a key past the range repeats the last row with weight 0)
         constexpr int U = VPL <= 4 ? 4 : (VPL <= 8 ? 2 : 1);
         for (int t = 0; t < nk; t += U) {
             float pt[U], x[U][VPL];

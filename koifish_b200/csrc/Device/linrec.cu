@@ -2,7 +2,7 @@
 //   (1) matrix-state recurrences with a decay per key channel: per head an fp32 state S [dk x dv] and, per token,
 //           S <- diag(g_t) S ;  then either   S <- S + k_t v_t^T                                   (gated linear attention)
 //                                     or      u = beta_t (v_t - S^T k_t),  S <- S + k_t u^T        (gated delta rule)
-//       and the read-out o_t = S^T q_t, which sees the token's own write.  The decay is formed in fp32 from a logit z while the
+//       and o_t = S^T q_t, taken after the write of token t.  The decay is formed in fp32 from a logit z while the
 //       token is staged: g = sigmoid(z + b)^(1/tau), or g = exp(-exp(A_h) softplus(z + b)).  q and k may be made unit vectors per head.
 //   (2) a real-gated linear recurrent unit over channels: block-diagonal gate matmuls r, i = sigmoid(W u_b + b), decay
 //       a = exp(-c r softplus(lam)), state s <- a s + sqrt(1 - a^2) i u, output s * y.
@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(256) kf_gated_scan_kernel(ScanArgs a) {
     for (int t0 = 0; t0 < a.T; t0 += TB) {
         const int nt = min(TB, a.T - t0);
         __syncthreads();
-        // four elements per thread and round: their global loads are issued together, then the decays are formed
+        // four elements per thread and step: their global loads are issued together, then the decays are formed
         for (int i0 = tid; i0 < nt * dk; i0 += 4 * blockDim.x) {
             float kv[4], qv[4], zv[4];
 #pragma unroll

@@ -1,6 +1,7 @@
-// Kivorax.hpp -- neurons of the Kivorax stack.  A layer is parallel: with h = norm(x), x <- x + mixer(h) + ff(h); then a per-layer token
-// input (a slice of a second embedding gates a small projection of x, RMS-normed and added), then the depth average: what the next
-// layer reads is a learned weighted sum of the embedding output and of every layer result so far.  Mixers: the gated delta rule and
+// Kivorax.hpp -- neurons of the Kivorax stack.  Every layer normalises once and both of its sublayers work from that copy, their
+// results going into the residual together (x += mixer(norm(x)) + ff(norm(x))); then comes a per-layer token input (a slice of a second
+// embedding gates a small projection of x, RMS-normed and added), then the depth average: the next layer does not read this layer's
+// result but a learned weighted sum of the embedding output and of all layer results so far.  Mixers: the gated delta rule and
 // gated linear attention (matrix-state recurrences, DeltaMixer / GLAMixer), and attention with a distance penalty beside a real-gated
 // linear recurrent unit (PairMixer).  Feed-forward: dense with biases, or routed experts weighted by the full softmax.  The residual,
 // norms, router, recurrences and attention scores are fp32; matmul inputs are written in the activation type.  The neurons use the
